@@ -1,0 +1,117 @@
+/* C ABI of libfmha_i8_sm100.so: the INT8 flash-attention forward pass for NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only, so the library can be bound from any language.  The C++ symbol
+ * gpuImpl::FMHAInferI8 (include/fmha_i8.h) is a thin shim over fmha_i8_sm100_infer.
+ *
+ * Conventions shared by every entry point
+ *   amax[5] = {q_amax, k_amax, v_amax, o_amax, s_max}   -- FMHAParamI8, inc/fmha_param_i8.h:10-17
+ *   desc[4] = {batch_num, seq_len, head_num, head_dim}  -- AttnDataDescriptor, inc/fmha_param_i8.h:3-8
+ *   q,k,v,o : int8 [B,H,S,D] contiguous, 16-byte aligned;  mask : int8 [B,S], 4-byte aligned,
+ *             non-zero byte = key masked out (inc/cpuSoftmax.hpp:24, inc/fmha_i8.cuh:189-192)
+ *   stream  : a cudaStream_t passed as void* (NULL = default stream)
+ *   return  : FMHA_I8_OK or a negative FMHA_I8_ERR_* decided on the host before anything is
+ *             launched.  Device-side trouble (a bounded wait that ran out) is reported through
+ *             fmha_i8_sm100_device_status().
+ * All device-pointer entry points enqueue on the stream and return without synchronising.
+ */
+#ifndef FMHA_I8_C_H_
+#define FMHA_I8_C_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  FMHA_I8_OK = 0,
+  FMHA_I8_ERR_NULL_POINTER = -1,   /* a required pointer is NULL */
+  FMHA_I8_ERR_BAD_SHAPE = -2,      /* head_dim not in {64,128}, seq_len not a multiple of 64 or > 32768, B/H < 1 */
+  FMHA_I8_ERR_MISALIGNED = -3,     /* q/k/v/o not 16-byte aligned or mask not 4-byte aligned */
+  FMHA_I8_ERR_NO_CUDA_CORE_PATH = -4, /* use_tcu == false: the reference's CUDA-core kernel is an empty stub */
+  FMHA_I8_ERR_WRONG_ARCH = -5,     /* current device is not compute capability 10.0 */
+  FMHA_I8_ERR_LAUNCH = -6,         /* the CUDA runtime rejected the launch or a copy */
+  FMHA_I8_ERR_DRIVER = -7,         /* tensor-map encoding failed or the driver entry point is missing */
+  FMHA_I8_ERR_BAD_SLICE = -8,      /* bh_begin/bh_count outside [0, B*H] */
+  FMHA_I8_ERR_BAD_AMAX = -9,       /* an amax is not a finite positive number */
+  FMHA_I8_ERR_TOO_LARGE = -10,     /* size beyond a stated maximum of the entry point */
+  FMHA_I8_ERR_DEVICE = -11         /* the device status words are non-zero (see device_status) */
+};
+
+/* words[0] of fmha_i8_sm100_device_status(): the bounded wait that ran out first. */
+enum {
+  FMHA_I8_DEV_OK = 0,
+  FMHA_I8_DEV_WAIT_Q_LOAD = 1,     /* MMA issuer waiting for the Q tiles */
+  FMHA_I8_DEV_WAIT_K_LOAD = 2,     /* MMA issuer waiting for a K stage */
+  FMHA_I8_DEV_WAIT_V_LOAD = 3,     /* MMA issuer waiting for a V stage */
+  FMHA_I8_DEV_WAIT_K_FREE = 4,     /* loader waiting for a K stage to be released */
+  FMHA_I8_DEV_WAIT_V_FREE = 5,     /* loader waiting for a V stage to be released */
+  FMHA_I8_DEV_WAIT_S_READY = 6,    /* softmax waiting for S = Q.K^T */
+  FMHA_I8_DEV_WAIT_P_READY = 7,    /* MMA issuer waiting for the quantised P */
+  FMHA_I8_DEV_WAIT_O_READY = 8,    /* softmax waiting for P.V */
+  FMHA_I8_DEV_WAIT_O_FREE = 9,     /* MMA issuer waiting for the previous P.V to be drained */
+  FMHA_I8_DEV_WAIT_DEBUG = 10      /* a wait inside a debug kernel */
+};
+
+#define FMHA_I8_FLAG_USE_TCU 1u    /* mirrors the reference's use_tcu argument; must be set */
+
+/* Replaces gpuImpl::FMHAInferI8 / LaunchFMHAInfer_TCU / FMHAInferKernel
+ * (src/fmha_i8.cu:157-173, :31-155, inc/fmha_i8.cuh:43-334): the whole forward pass
+ * O8 = requant(softmax_tile128(Q8 K8^T * q_amax k_amax / (127^2 sqrt(D))) V8). */
+int fmha_i8_sm100_infer(void* stream, const float amax[5], const int desc[4],
+                        const void* q, const void* k, const void* v, const void* mask, void* o,
+                        unsigned flags);
+
+/* The same computation for heads [bh_begin, bh_begin + bh_count) of the flattened batch*head
+ * axis, for partitioning one problem over several GPUs.  q,k,v,o point at the FIRST head of the
+ * slice (each GPU holds only its slice); mask is the whole [B,S] mask and desc the whole shape.
+ * The reference has no counterpart: its grid is (batch, head) on one GPU (src/fmha_i8.cu:43). */
+int fmha_i8_sm100_infer_slice(void* stream, const float amax[5], const int desc[4],
+                              const void* q, const void* k, const void* v, const void* mask, void* o,
+                              int bh_begin, int bh_count, unsigned flags);
+
+/* End-to-end form of the caller in test_fmha_i8.cpp:165-178,204,236: HOST buffers in, HOST
+ * buffer out.  Copies q,k,v,mask to device staging buffers owned by the library (grown on demand,
+ * kept for reuse), runs the forward pass, copies o back and synchronises.  Pinned host memory
+ * makes the copies asynchronous to each other; pageable memory works too. */
+int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4],
+                             const void* host_q, const void* host_k, const void* host_v,
+                             const void* host_mask, void* host_o, unsigned flags);
+
+/* Debug: S_int32[bh, i, j] = sum_d q[bh,i,d] k[bh,j,d] written as int32 [B*H, S, S] through the
+ * same TMA + tensor-core stage the forward pass uses (GEMM 1, inc/fmha_i8.cuh:120-172).  For
+ * bit-exact checks against cpuGEMM<int32_t,int32_t,int8_t,int32_t>; small shapes only. */
+int fmha_i8_sm100_debug_qk(void* stream, const int desc[4], const void* q, const void* k, int32_t* s_out);
+
+/* Debug: O_int32[bh, i, d] = sum_j p[bh,i,j] v[bh,j,d] as int32 [B*H, S, D] with p int8 [B*H,S,S],
+ * through the P.V stage of the forward pass (GEMM 2, inc/fmha_i8.cuh:255-296).
+ * variant 0: P handed to the tensor core from tensor memory; variant 1: from shared memory. */
+int fmha_i8_sm100_debug_pv(void* stream, const int desc[4], const void* p, const void* v,
+                           int32_t* o_out, unsigned variant);
+
+/* Debug: the forward pass on CUDA cores (dp4a), one thread per query row, with the operation
+ * order of the quantised CPU oracle.  An on-device cross-check for full-size shapes, never
+ * selected by the product entry points.  Same arguments as fmha_i8_sm100_infer. */
+int fmha_i8_sm100_debug_simt(void* stream, const float amax[5], const int desc[4],
+                             const void* q, const void* k, const void* v, const void* mask, void* o);
+
+/* Synchronises the current device, copies out and clears the eight device status words.
+ * words[0] == 0 means no kernel of this library gave up on a bounded wait since the last call.
+ * Otherwise words[0] = which wait gave up (FMHA_I8_DEV_*), words[1] = block index, words[2] = warp,
+ * words[3] = key-tile counter of the first failure.
+ * Returns FMHA_I8_OK, FMHA_I8_ERR_DEVICE when words[0] != 0, or FMHA_I8_ERR_LAUNCH. */
+int fmha_i8_sm100_device_status(unsigned words[8]);
+
+/* Status of the most recent call on this host thread (what the void C++ shim could not return). */
+int fmha_i8_sm100_last_status(void);
+const char* fmha_i8_sm100_status_string(int status);
+
+/* Number of kernels this library has launched in this process (all entry points). */
+unsigned long long fmha_i8_sm100_launch_count(void);
+
+int fmha_i8_sm100_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FMHA_I8_C_H_ */

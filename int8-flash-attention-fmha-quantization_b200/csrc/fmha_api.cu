@@ -1,0 +1,393 @@
+// Host side of libfmha_i8_sm100.so: argument checks, tensor-map encoding, launches and the C ABI
+// declared in include/fmha_i8_c.h.  Replaces the reference project's launcher
+// (src/fmha_i8.cu:31-173): one runtime-shaped kernel instead of a table of compile-time shapes.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/fmha_i8_c.h"
+#include "fmha_debug_sm100.cuh"
+#include "fmha_fwd_sm100.cuh"
+
+namespace {
+
+using namespace fmha;
+
+__device__ unsigned g_status_words[8];
+
+thread_local int t_last_status = FMHA_I8_OK;
+std::atomic<unsigned long long> g_launch_count{0};
+
+int finish(int status) {
+  t_last_status = status;
+  return status;
+}
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceInfo {
+  int checked = 0;      // 0 = not yet, 1 = sm_100, -1 = something else
+  unsigned* status = nullptr;
+  bool attr_set = false;
+};
+DeviceInfo g_dev[kMaxDevices];
+std::mutex g_dev_mutex;
+
+// Returns the per-device record of the current device (compute capability check, address of the
+// status words, one-time kernel attributes), or nullptr with *err set.
+DeviceInfo* current_device(int* err) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { *err = FMHA_I8_ERR_LAUNCH; return nullptr; }
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  DeviceInfo& d = g_dev[dev];
+  if (d.checked == 0) {
+    int major = 0, minor = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess) {
+      *err = FMHA_I8_ERR_LAUNCH;
+      return nullptr;
+    }
+    d.checked = (major == 10 && minor == 0) ? 1 : -1;
+  }
+  if (d.checked < 0) { *err = FMHA_I8_ERR_WRONG_ARCH; return nullptr; }
+  if (!d.status) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_status_words) != cudaSuccess) { *err = FMHA_I8_ERR_LAUNCH; return nullptr; }
+    d.status = static_cast<unsigned*>(ptr);
+  }
+  return &d;
+}
+
+template <int D> size_t fwd_smem_bytes() {
+  return 1024 + FwdCfg<D>::kTilesBytesTotal + sizeof(FwdCtl<FwdCfg<D>::kStages>);
+}
+template <int D> size_t qk_smem_bytes() { return 1024 + 2 * kTile * D + sizeof(DebugCtl); }
+template <int D> size_t pv_smem_bytes() { return 1024 + kTile * D + kTile * kTile + sizeof(DebugCtl); }
+
+int set_kernel_attributes(DeviceInfo* d) {
+  if (d->attr_set) return FMHA_I8_OK;
+  cudaError_t e = cudaSuccess;
+  auto set = [&](const void* fn, size_t bytes) {
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+  };
+  set(reinterpret_cast<const void*>(&fmha_fwd_kernel<64>), fwd_smem_bytes<64>());
+  set(reinterpret_cast<const void*>(&fmha_fwd_kernel<128>), fwd_smem_bytes<128>());
+  set(reinterpret_cast<const void*>(&debug_qk_kernel<64>), qk_smem_bytes<64>());
+  set(reinterpret_cast<const void*>(&debug_qk_kernel<128>), qk_smem_bytes<128>());
+  set(reinterpret_cast<const void*>(&debug_pv_kernel<64, true>), pv_smem_bytes<64>());
+  set(reinterpret_cast<const void*>(&debug_pv_kernel<64, false>), pv_smem_bytes<64>());
+  set(reinterpret_cast<const void*>(&debug_pv_kernel<128, true>), pv_smem_bytes<128>());
+  set(reinterpret_cast<const void*>(&debug_pv_kernel<128, false>), pv_smem_bytes<128>());
+  if (e != cudaSuccess) { cudaGetLastError(); return FMHA_I8_ERR_LAUNCH; }
+  d->attr_set = true;
+  return FMHA_I8_OK;
+}
+
+// cuTensorMapEncodeTiled, fetched through the runtime so the library has no link-time libcuda dependency.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+// int8 tensor [n_heads, S, D] seen as a 3-D map (D innermost) with boxes of 128 rows of one head.
+// Rows past S are zero-filled by the copy engine instead of running into the next head.
+int make_map(CUtensorMap* map, const void* base, int n_heads, int S, int D) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return FMHA_I8_ERR_DRIVER;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(n_heads)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S) * D};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(D), static_cast<cuuint32_t>(kTile), 1u};
+  const cuuint32_t estr[3] = {1u, 1u, 1u};
+  const CUtensorMapSwizzle sw = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FMHA_I8_OK : FMHA_I8_ERR_DRIVER;
+}
+
+bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int check_shape(const int desc[4]) {
+  const int B = desc[0], S = desc[1], H = desc[2], D = desc[3];
+  if (B < 1 || H < 1 || S < 64 || S > kMaxSeq || (S % 64) != 0) return FMHA_I8_ERR_BAD_SHAPE;
+  if (D != 64 && D != 128) return FMHA_I8_ERR_BAD_SHAPE;
+  if (static_cast<long long>(B) * H > 0x7FFFFFFFLL / 2) return FMHA_I8_ERR_BAD_SHAPE;
+  return FMHA_I8_OK;
+}
+
+// The reference evaluates 1/sqrt(head_dim) with a Newton iteration carried in float
+// (inc/fmha_i8.cuh:13-34,71); the same recurrence gives the same constant.
+float reference_row_scale(int D) {
+  const float x = static_cast<float>(D);
+  float curr = x, prev = 0.f;
+  while (curr != prev) {
+    const float next = static_cast<float>(0.5 * (static_cast<double>(curr) + static_cast<double>(x / curr)));
+    prev = curr;
+    curr = next;
+  }
+  return 1.0f / curr;
+}
+
+int fill_params(FwdParams* p, const float amax[5], const int desc[4]) {
+  for (int i = 0; i < 4; ++i)
+    if (!(amax[i] > 0.f) || !std::isfinite(amax[i])) return FMHA_I8_ERR_BAD_AMAX;
+  p->row_scale = reference_row_scale(desc[3]);
+  p->scale_qk = amax[0] * amax[1] / (127.f * 127.f);
+  p->scale_v_out = amax[2] * (1.0f / (amax[3] * 128.f));
+  const float c2 = static_cast<float>(static_cast<double>(p->row_scale) * static_cast<double>(p->scale_qk) * 1.4426950408889634);
+  uint32_t bits;
+  std::memcpy(&bits, &c2, 4);
+  bits &= 0xFFFFFFFCu;
+  std::memcpy(&p->c2, &bits, 4);
+  p->c2_bias = static_cast<float>(static_cast<double>(kMagic) * static_cast<double>(p->c2));
+  if (!(p->c2 > 0.f) || !std::isfinite(p->c2_bias)) return FMHA_I8_ERR_BAD_AMAX;
+  return FMHA_I8_OK;
+}
+
+template <int D>
+int launch_fwd(cudaStream_t stream, DeviceInfo* dev, FwdParams p, const void* q, const void* k, const void* v) {
+  CUtensorMap mq, mk, mv;
+  int st;
+  if ((st = make_map(&mq, q, p.bh_count, p.S, D)) != FMHA_I8_OK) return st;
+  if ((st = make_map(&mk, k, p.bh_count, p.S, D)) != FMHA_I8_OK) return st;
+  if ((st = make_map(&mv, v, p.bh_count, p.S, D)) != FMHA_I8_OK) return st;
+  const unsigned grid = static_cast<unsigned>(p.bh_count) * static_cast<unsigned>(p.q_pairs);
+  fmha_fwd_kernel<D><<<grid, kFwdThreads, fwd_smem_bytes<D>(), stream>>>(mq, mk, mv, p);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH;
+}
+
+int infer_slice_impl(void* stream, const float amax[5], const int desc[4], const void* q, const void* k,
+                     const void* v, const void* mask, void* o, int bh_begin, int bh_count, unsigned flags) {
+  if (!amax || !desc || !q || !k || !v || !mask || !o) return FMHA_I8_ERR_NULL_POINTER;
+  if (!(flags & FMHA_I8_FLAG_USE_TCU)) return FMHA_I8_ERR_NO_CUDA_CORE_PATH;
+  int st = check_shape(desc);
+  if (st != FMHA_I8_OK) return st;
+  const long long BH = static_cast<long long>(desc[0]) * desc[2];
+  if (bh_begin < 0 || bh_count < 1 || static_cast<long long>(bh_begin) + bh_count > BH) return FMHA_I8_ERR_BAD_SLICE;
+  if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(o, 16) || !aligned(mask, 4))
+    return FMHA_I8_ERR_MISALIGNED;
+  FwdParams p{};
+  if ((st = fill_params(&p, amax, desc)) != FMHA_I8_OK) return st;
+  int err = FMHA_I8_OK;
+  DeviceInfo* dev = current_device(&err);
+  if (!dev) return err;
+  if ((st = set_kernel_attributes(dev)) != FMHA_I8_OK) return st;
+  p.mask = static_cast<const int8_t*>(mask);
+  p.o = static_cast<int8_t*>(o);
+  p.S = desc[1];
+  p.H = desc[2];
+  p.bh_begin = bh_begin;
+  p.bh_count = bh_count;
+  p.q_pairs = (p.S + 2 * kTile - 1) / (2 * kTile);
+  p.status = dev->status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return desc[3] == 128 ? launch_fwd<128>(s, dev, p, q, k, v) : launch_fwd<64>(s, dev, p, q, k, v);
+}
+
+// Device staging buffers of fmha_i8_sm100_infer_host, one set per device, grown on demand.
+struct HostStaging {
+  void* q = nullptr; void* k = nullptr; void* v = nullptr; void* o = nullptr; void* mask = nullptr;
+  size_t tensor_cap = 0, mask_cap = 0;
+  cudaStream_t stream = nullptr;
+};
+HostStaging g_staging[kMaxDevices];
+std::mutex g_staging_mutex;
+
+}  // namespace
+
+extern "C" {
+
+int fmha_i8_sm100_infer(void* stream, const float amax[5], const int desc[4], const void* q, const void* k,
+                        const void* v, const void* mask, void* o, unsigned flags) {
+  if (!desc) return finish(FMHA_I8_ERR_NULL_POINTER);
+  const long long BH = static_cast<long long>(desc[0]) * desc[2];
+  if (BH < 1 || BH > 0x7FFFFFFFLL) return finish(FMHA_I8_ERR_BAD_SHAPE);
+  return finish(infer_slice_impl(stream, amax, desc, q, k, v, mask, o, 0, static_cast<int>(BH), flags));
+}
+
+int fmha_i8_sm100_infer_slice(void* stream, const float amax[5], const int desc[4], const void* q, const void* k,
+                              const void* v, const void* mask, void* o, int bh_begin, int bh_count, unsigned flags) {
+  return finish(infer_slice_impl(stream, amax, desc, q, k, v, mask, o, bh_begin, bh_count, flags));
+}
+
+int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void* host_q, const void* host_k,
+                             const void* host_v, const void* host_mask, void* host_o, unsigned flags) {
+  if (!amax || !desc || !host_q || !host_k || !host_v || !host_mask || !host_o) return finish(FMHA_I8_ERR_NULL_POINTER);
+  int st = check_shape(desc);
+  if (st != FMHA_I8_OK) return finish(st);
+  int dev_id = 0;
+  if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id >= kMaxDevices) return finish(FMHA_I8_ERR_LAUNCH);
+  const size_t tensor_bytes = static_cast<size_t>(desc[0]) * desc[2] * desc[1] * desc[3];
+  const size_t mask_bytes = static_cast<size_t>(desc[0]) * desc[1];
+  std::lock_guard<std::mutex> lock(g_staging_mutex);
+  HostStaging& s = g_staging[dev_id];
+  if (!s.stream && cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess) return finish(FMHA_I8_ERR_LAUNCH);
+  if (s.tensor_cap < tensor_bytes) {
+    cudaFree(s.q); cudaFree(s.k); cudaFree(s.v); cudaFree(s.o);
+    s.q = s.k = s.v = s.o = nullptr;
+    s.tensor_cap = 0;
+    if (cudaMalloc(&s.q, tensor_bytes) != cudaSuccess || cudaMalloc(&s.k, tensor_bytes) != cudaSuccess ||
+        cudaMalloc(&s.v, tensor_bytes) != cudaSuccess || cudaMalloc(&s.o, tensor_bytes) != cudaSuccess) {
+      cudaGetLastError();
+      return finish(FMHA_I8_ERR_LAUNCH);
+    }
+    s.tensor_cap = tensor_bytes;
+  }
+  if (s.mask_cap < mask_bytes) {
+    cudaFree(s.mask);
+    s.mask = nullptr;
+    s.mask_cap = 0;
+    if (cudaMalloc(&s.mask, mask_bytes) != cudaSuccess) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
+    s.mask_cap = mask_bytes;
+  }
+  cudaError_t e = cudaMemcpyAsync(s.q, host_q, tensor_bytes, cudaMemcpyHostToDevice, s.stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(s.k, host_k, tensor_bytes, cudaMemcpyHostToDevice, s.stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(s.mask, host_mask, mask_bytes, cudaMemcpyHostToDevice, s.stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(s.v, host_v, tensor_bytes, cudaMemcpyHostToDevice, s.stream);
+  if (e != cudaSuccess) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
+  st = infer_slice_impl(s.stream, amax, desc, s.q, s.k, s.v, s.mask, s.o, 0, desc[0] * desc[2], flags);
+  if (st != FMHA_I8_OK) return finish(st);
+  e = cudaMemcpyAsync(host_o, s.o, tensor_bytes, cudaMemcpyDeviceToHost, s.stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s.stream);
+  if (e != cudaSuccess) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
+  return finish(FMHA_I8_OK);
+}
+
+int fmha_i8_sm100_debug_qk(void* stream, const int desc[4], const void* q, const void* k, int32_t* s_out) {
+  if (!desc || !q || !k || !s_out) return finish(FMHA_I8_ERR_NULL_POINTER);
+  int st = check_shape(desc);
+  if (st != FMHA_I8_OK) return finish(st);
+  if (!aligned(q, 16) || !aligned(k, 16) || !aligned(s_out, 4)) return finish(FMHA_I8_ERR_MISALIGNED);
+  int err = FMHA_I8_OK;
+  DeviceInfo* dev = current_device(&err);
+  if (!dev) return finish(err);
+  if ((st = set_kernel_attributes(dev)) != FMHA_I8_OK) return finish(st);
+  const int BH = desc[0] * desc[2], S = desc[1], D = desc[3];
+  if (BH > 65535) return finish(FMHA_I8_ERR_TOO_LARGE);
+  CUtensorMap mq, mk;
+  if ((st = make_map(&mq, q, BH, S, D)) != FMHA_I8_OK) return finish(st);
+  if ((st = make_map(&mk, k, BH, S, D)) != FMHA_I8_OK) return finish(st);
+  const int nt = (S + kTile - 1) / kTile;
+  const dim3 grid(nt, nt, BH);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 128) debug_qk_kernel<128><<<grid, 128, qk_smem_bytes<128>(), s>>>(mq, mk, s_out, S, dev->status);
+  else debug_qk_kernel<64><<<grid, 128, qk_smem_bytes<64>(), s>>>(mq, mk, s_out, S, dev->status);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return finish(cudaGetLastError() == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH);
+}
+
+int fmha_i8_sm100_debug_pv(void* stream, const int desc[4], const void* p, const void* v, int32_t* o_out,
+                           unsigned variant) {
+  if (!desc || !p || !v || !o_out) return finish(FMHA_I8_ERR_NULL_POINTER);
+  int st = check_shape(desc);
+  if (st != FMHA_I8_OK) return finish(st);
+  if (!aligned(p, 16) || !aligned(v, 16) || !aligned(o_out, 4)) return finish(FMHA_I8_ERR_MISALIGNED);
+  if (variant > 1) return finish(FMHA_I8_ERR_BAD_SHAPE);
+  int err = FMHA_I8_OK;
+  DeviceInfo* dev = current_device(&err);
+  if (!dev) return finish(err);
+  if ((st = set_kernel_attributes(dev)) != FMHA_I8_OK) return finish(st);
+  const int BH = desc[0] * desc[2], S = desc[1], D = desc[3];
+  if (BH > 65535) return finish(FMHA_I8_ERR_TOO_LARGE);
+  CUtensorMap mv;
+  if ((st = make_map(&mv, v, BH, S, D)) != FMHA_I8_OK) return finish(st);
+  const dim3 grid((S + kTile - 1) / kTile, BH);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int8_t* p8 = static_cast<const int8_t*>(p);
+  if (D == 128) {
+    if (variant == 0) debug_pv_kernel<128, true><<<grid, 128, pv_smem_bytes<128>(), s>>>(mv, p8, o_out, S, dev->status);
+    else debug_pv_kernel<128, false><<<grid, 128, pv_smem_bytes<128>(), s>>>(mv, p8, o_out, S, dev->status);
+  } else {
+    if (variant == 0) debug_pv_kernel<64, true><<<grid, 128, pv_smem_bytes<64>(), s>>>(mv, p8, o_out, S, dev->status);
+    else debug_pv_kernel<64, false><<<grid, 128, pv_smem_bytes<64>(), s>>>(mv, p8, o_out, S, dev->status);
+  }
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return finish(cudaGetLastError() == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH);
+}
+
+int fmha_i8_sm100_debug_simt(void* stream, const float amax[5], const int desc[4], const void* q, const void* k,
+                             const void* v, const void* mask, void* o) {
+  if (!amax || !desc || !q || !k || !v || !mask || !o) return finish(FMHA_I8_ERR_NULL_POINTER);
+  int st = check_shape(desc);
+  if (st != FMHA_I8_OK) return finish(st);
+  if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(o, 16)) return finish(FMHA_I8_ERR_MISALIGNED);
+  FwdParams p{};
+  if ((st = fill_params(&p, amax, desc)) != FMHA_I8_OK) return finish(st);
+  int err = FMHA_I8_OK;
+  if (!current_device(&err)) return finish(err);
+  const int BH = desc[0] * desc[2], S = desc[1], H = desc[2], D = desc[3];
+  if (BH > 65535) return finish(FMHA_I8_ERR_TOO_LARGE);
+  const dim3 grid((S + kTile - 1) / kTile, BH);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int8_t* q8 = static_cast<const int8_t*>(q);
+  const int8_t* k8 = static_cast<const int8_t*>(k);
+  const int8_t* v8 = static_cast<const int8_t*>(v);
+  const int8_t* m8 = static_cast<const int8_t*>(mask);
+  int8_t* o8 = static_cast<int8_t*>(o);
+  if (D == 128) simt_check_kernel<128><<<grid, 128, 0, s>>>(q8, k8, v8, m8, o8, S, H, 0, p.row_scale, p.scale_qk, p.scale_v_out);
+  else simt_check_kernel<64><<<grid, 128, 0, s>>>(q8, k8, v8, m8, o8, S, H, 0, p.row_scale, p.scale_qk, p.scale_v_out);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return finish(cudaGetLastError() == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH);
+}
+
+int fmha_i8_sm100_device_status(unsigned words[8]) {
+  if (!words) return finish(FMHA_I8_ERR_NULL_POINTER);
+  if (cudaDeviceSynchronize() != cudaSuccess) { return finish(FMHA_I8_ERR_LAUNCH); }
+  if (cudaMemcpyFromSymbol(words, g_status_words, sizeof(unsigned) * 8) != cudaSuccess) return finish(FMHA_I8_ERR_LAUNCH);
+  const unsigned zeros[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (cudaMemcpyToSymbol(g_status_words, zeros, sizeof zeros) != cudaSuccess) return finish(FMHA_I8_ERR_LAUNCH);
+  return finish(words[0] == 0u ? FMHA_I8_OK : FMHA_I8_ERR_DEVICE);
+}
+
+int fmha_i8_sm100_last_status(void) { return t_last_status; }
+
+const char* fmha_i8_sm100_status_string(int status) {
+  switch (status) {
+    case FMHA_I8_OK: return "ok";
+    case FMHA_I8_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case FMHA_I8_ERR_BAD_SHAPE: return "unsupported shape (head_dim must be 64 or 128, seq_len a multiple of 64 up to 32768)";
+    case FMHA_I8_ERR_MISALIGNED: return "q/k/v/o must be 16-byte aligned and the mask 4-byte aligned";
+    case FMHA_I8_ERR_NO_CUDA_CORE_PATH: return "use_tcu == false is not supported (the reference's CUDA-core kernel is an empty stub)";
+    case FMHA_I8_ERR_WRONG_ARCH: return "the current device is not compute capability 10.0 (B200)";
+    case FMHA_I8_ERR_LAUNCH: return "the CUDA runtime reported an error";
+    case FMHA_I8_ERR_DRIVER: return "tensor-map encoding failed";
+    case FMHA_I8_ERR_BAD_SLICE: return "bh_begin/bh_count outside the batch*head range";
+    case FMHA_I8_ERR_BAD_AMAX: return "amax values must be finite and positive";
+    case FMHA_I8_ERR_TOO_LARGE: return "size beyond the maximum of this entry point";
+    case FMHA_I8_ERR_DEVICE: return "a device-side bounded wait ran out (see fmha_i8_sm100_device_status)";
+    default: return "unknown status";
+  }
+}
+
+unsigned long long fmha_i8_sm100_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
+
+int fmha_i8_sm100_version(void) { return 100; }
+
+}  // extern "C"
+
+// The reference project's C++ entry point (inc/fmha_i8.h:5-17), kept symbol-for-symbol.
+#include "../../include/fmha_i8.h"
+namespace gpuImpl {
+void FMHAInferI8(cudaStream_t stream, FMHAParamI8 fmha_param, AttnDataDescriptor attn_desc, const void* q,
+                 const void* k, const void* v, const void* padding_mask, void* o, const bool use_tcu) {
+  const float amax[5] = {fmha_param.q_amax, fmha_param.k_amax, fmha_param.v_amax, fmha_param.o_amax, fmha_param.s_max};
+  const int desc[4] = {attn_desc.batch_num, attn_desc.seq_len, attn_desc.head_num, attn_desc.head_dim};
+  const int st = fmha_i8_sm100_infer(stream, amax, desc, q, k, v, padding_mask, o, use_tcu ? FMHA_I8_FLAG_USE_TCU : 0u);
+  if (st != FMHA_I8_OK) std::fprintf(stderr, "gpuImpl::FMHAInferI8: %s (status %d)\n", fmha_i8_sm100_status_string(st), st);
+}
+}  // namespace gpuImpl
