@@ -1,0 +1,317 @@
+#!/usr/bin/env python
+"""Benchmark of the INT8 flash-attention forward path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config C3] [--impl ours|reference]
+
+One "step" is one forward pass over one batch of synthetic int8 Q,K,V (seeded; the reference
+project ships no dataset).  The default workload is C3 (B=8,H=32,S=2048,D=128), the shape the
+throughput target is quoted on.  With N > 1 (launched under torchrun, one rank per GPU) every rank
+runs the whole workload on its own GPU -- the path shards over batch*head with no exchange step,
+so there is no collective on the data path ("weak" scaling); NCCL is used only for the barrier and
+the max-over-ranks of the device time.
+
+Prints ONE JSON line on rank 0:
+  value      effective INT8 TOPS = N * 4*B*H*S^2*D / t, inputs resident in HBM, CUDA-event timed
+  e2e        the same metric through fmha_i8_sm100_infer_host: pinned HOST buffers in and out,
+             host<->device copies inside the timed region
+  roofline   dominant kernel against the dense-INT8 tensor peak (2 x the measured dense bf16
+             cuBLAS rate of this pool's B200s; kind::i8 runs at twice the bf16 rate)
+  cpu_baseline  the reference project's CPU path (oracle/_ref) on a bounded sample of heads
+
+--impl reference times the reference project's own CPU implementation of the path instead.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "effective INT8 TOPS (4*B*H*S^2*D / t) per job"
+UNIT = "TOPS"
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"bf16_tflops": float(p["bf16_tflops"]), "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
+    return {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [x.strip() for x in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        mhz = sorted(float(s[0]) for s in self.samples)
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": float(self.samples[0][1]), "reasons": reasons,
+                "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        ids = [x for x in vis.split(",") if x != ""]
+        if local_rank < len(ids) and ids[local_rank].isdigit():
+            return int(ids[local_rank])
+    return local_rank
+
+
+def cpu_baseline(workload, seconds_hint=10.0):
+    """The reference project's fp32 CPU path (its unchanged templates, one single-slice call chain per
+    head, heads spread over all host threads) on a bounded sample of whole heads of `workload`."""
+    import numpy as np
+    import __graft_entry__ as ge
+    oracle = ge.load_oracle()
+    cores = oracle.n_threads_default()
+    w = workload
+    per_head_ops = 4.0 * w.S * w.S * w.D
+    est_rate = 1.5e9  # ops/s/thread, the order of magnitude of the unvectorised triple loop
+    heads = max(1, min(w.B * w.H, int(round(seconds_hint * est_rate * cores / per_head_ops))))
+    if heads >= cores:
+        heads = (heads // cores) * cores       # whole rounds of one head per thread
+    rng = np.random.default_rng(2023)
+    q, k, v = (rng.standard_normal((1, heads, w.S, w.D), dtype=np.float32) for _ in range(3))
+    mask = np.zeros((1, w.S), np.int8)
+    if w.valid_choices is not None:
+        mask[0, min(w.valid_choices):] = 1
+    if oracle.ref_cpu_available(native=True):
+        kind = "reference"
+        t0 = time.perf_counter()
+        oracle.ref_fp32_attention(q, k, v, mask, batched=False, threads=cores, native=True)
+        dt = time.perf_counter() - t0
+    else:
+        kind = "port"
+        t0 = time.perf_counter()
+        oracle.fp32_attention(q, k, v, mask, threads=cores)
+        dt = time.perf_counter() - t0
+    return {"value": heads * per_head_ops / dt / 1e12, "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": f"{heads} of {w.B * w.H} heads of {w.name} (S={w.S}, D={w.D}), fp32 cpuGEMM/cpuSoftmax path, "
+                      f"{dt:.2f} s, -O3 -march=x86-64-v3",
+            "seconds": dt, "heads": heads}
+
+
+def run_reference_arm(args, workload):
+    """--impl reference: the reference's CPU implementation of the path, all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    import __graft_entry__ as ge
+    oracle = ge.load_oracle()
+    cores = oracle.n_threads_default()
+    w = workload
+    per_head_ops = 4.0 * w.S * w.S * w.D
+    heads = min(w.B * w.H, cores)          # one whole head per host thread and step
+    rng = np.random.default_rng(2023)
+    q, k, v = (rng.standard_normal((1, heads, w.S, w.D), dtype=np.float32) for _ in range(3))
+    mask = np.zeros((1, w.S), np.int8)
+    if w.valid_choices is not None:
+        mask[0, min(w.valid_choices):] = 1
+    native = oracle.ref_cpu_available(native=True)
+    kind = "reference" if native else "port"
+
+    def step():
+        if native:
+            oracle.ref_fp32_attention(q, k, v, mask, batched=False, threads=cores, native=True)
+        else:
+            oracle.fp32_attention(q, k, v, mask, threads=cores)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / max(args.steps, 1)
+    value = heads * per_head_ops / dt / 1e12
+    sample = (f"each step = {heads} of {w.B * w.H} heads of {w.name} (S={w.S}, D={w.D}), one head per host thread, "
+              f"reference fp32 cpuGEMM/cpuSoftmax path")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{w.name}: B={w.B} H={w.H} S={w.S} D={w.D}", "sampled_heads_per_step": heads},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default="C3")
+    ap.add_argument("--batch", type=int, default=0, help="override the batch size of the workload (profiling)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seed", type=int, default=2023)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=0)
+    args = ap.parse_args()
+
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    import importlib
+    wl = importlib.import_module("int8_fmha_b200.workloads")
+    w = wl.CONFIGS[args.config]
+    if args.batch:
+        w = w.with_batch(args.batch)
+
+    if args.impl == "reference":
+        run_reference_arm(args, w)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    n_gpus = max(world, 1)
+    args.warmup = max(args.warmup, 3)
+
+    pkg.lib()  # fails loudly if the CUDA library is missing
+    # ---- inputs: generated and quantised on the device, o_amax calibrated from an fp32 attention
+    data = wl.make_int8_torch(w, args.seed + 101 * rank, dev, want_fp32=True)
+    _, o_amax = wl.fp32_attention_torch(data["q"], data["k"], data["v"], data["mask"])
+    for n in ("q", "k", "v"):
+        del data[n]
+    torch.cuda.empty_cache()
+    q8, k8, v8, mask = data["q8"], data["k8"], data["v8"], data["mask"]
+    o8 = torch.empty_like(q8)
+    param = pkg.FMHAParamI8(*data["amax"], o_amax, 1.0)
+    desc = pkg.AttnDataDescriptor(w.B, w.S, w.H, w.D)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        pkg.FMHAInferI8(stream, param, desc, q8, k8, v8, mask, o8, True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    st, words = pkg.device_status()
+    if st != pkg.OK:
+        raise RuntimeError(f"device status after warm-up: {words}")
+
+    launches0 = pkg.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        barrier()
+        ev0.record(stream)
+        for _ in range(args.steps):
+            step()
+        ev1.record(stream)
+        barrier()
+    launches = pkg.launch_count() - launches0
+    ms_total = ev0.elapsed_time(ev1)
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    st, words = pkg.device_status()
+    if st != pkg.OK:
+        raise RuntimeError(f"device status after the timed region: {words}")
+    value = n_gpus * w.ops / (ms_step * 1e-3) / 1e12
+
+    # ---- roofline of the dominant (only) kernel: one launch per step
+    peaks = read_peaks()
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    local_ms_launch = ms_total / max(launches, 1)
+    achieved = w.ops / (local_ms_launch * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s", "frac": achieved / int8_peak,
+                "traffic": None, "kernel": f"fmha_fwd_kernel<{w.D}>",
+                "peak_source": f"2 x {peaks['source']} dense bf16 ({peaks['bf16_tflops']} TFLOP/s): kind::i8 issues at twice the bf16 rate",
+                "hbm_gbs_achieved": w.bytes / (local_ms_launch * 1e-3) / 1e9, "hbm_gbs_peak": peaks["hbm_gbs"]}
+
+    # ---- end to end through the host-buffer entry point (pinned host memory, copies inside)
+    e2e = None
+    if not args.no_e2e:
+        hq, hk, hv, hm = (x.cpu().pin_memory() for x in (q8, k8, v8, mask))
+        ho = torch.empty_like(hq).pin_memory()
+        n_e2e = args.e2e_steps or max(3, min(args.steps, 10))
+        for _ in range(2):
+            pkg.FMHAInferI8Host(param, desc, hq, hk, hv, hm, ho)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(n_e2e):
+            pkg.FMHAInferI8Host(param, desc, hq, hk, hv, hm, ho)
+        dt = (time.perf_counter() - t0) / n_e2e
+        tt = torch.tensor([dt], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt = float(tt.item())
+        same = bool(torch.equal(ho, o8.cpu()))
+        e2e = {"value": n_gpus * w.ops / dt / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(3 * q8.numel() + mask.numel()),
+               "d2h_bytes_per_step": int(o8.numel()), "ms_per_step": dt * 1e3, "steps": n_e2e,
+               "matches_device_resident_result": same}
+
+    cpu = None
+    if rank == 0 and n_gpus == 1 and not args.no_cpu:
+        try:
+            cpu = cpu_baseline(w)
+        except Exception as exc:  # the baseline is a reported extra, never a reason to lose the GPU numbers
+            cpu = {"value": None, "unit": UNIT, "cores": None, "kind": "unavailable", "sample": repr(exc)}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+                "data": "synthetic",
+                "config": {"workload": f"{w.name}: B={w.B} H={w.H} S={w.S} D={w.D} per GPU", "mask": "none" if w.valid_choices is None else f"valid lengths {w.valid_choices}",
+                           "l2": "inputs larger than L2 (Q,K,V,O = %.0f MB)" % (w.bytes / 1e6), "seed": args.seed,
+                           "parallelism": f"{n_gpus} x whole workload, no collective"},
+                "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
+                "cpu_baseline": cpu, "pct_of_int8_peak": 100.0 * achieved / int8_peak}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

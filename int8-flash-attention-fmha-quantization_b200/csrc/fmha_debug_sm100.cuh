@@ -34,7 +34,7 @@ debug_qk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(smem_u32(&ctl->done), 1);
     mbar_init_fence();
   }
-  if (warp == 0) { tmem_alloc(smem_u32(&ctl->tmem_base), 128); tmem_relinquish(); }
+  if (warp == 0) { __syncwarp(); tmem_alloc(smem_u32(&ctl->tmem_base), 128); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -67,7 +67,6 @@ debug_qk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     for (int c = 0; c < 4; ++c) {
       uint32_t r[32];
       tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c * 32, r);
-      tmem_wait_ld();
       if (row < S) {
         int32_t* dst = s_out + (static_cast<int64_t>(bh) * S + row) * S + kt * kTile + c * 32;
 #pragma unroll
@@ -108,7 +107,7 @@ debug_pv_kernel(const __grid_constant__ CUtensorMap map_v, const int8_t* p8, int
     mbar_init(smem_u32(&ctl->done), 1);
     mbar_init_fence();
   }
-  if (warp == 0) { tmem_alloc(smem_u32(&ctl->tmem_base), 256); tmem_relinquish(); }
+  if (warp == 0) { __syncwarp(); tmem_alloc(smem_u32(&ctl->tmem_base), 256); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -177,7 +176,6 @@ debug_pv_kernel(const __grid_constant__ CUtensorMap map_v, const int8_t* p8, int
     for (int c = 0; c < D / 32; ++c) {
       uint32_t r[32];
       tmem_ld32(tmem_base + lane_field + 128 + c * 32, r);
-      tmem_wait_ld();
       if (row < S) {
         int32_t* dst = o_out + (static_cast<int64_t>(bh) * S + row) * D + c * 32;
 #pragma unroll

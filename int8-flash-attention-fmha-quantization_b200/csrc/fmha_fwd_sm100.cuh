@@ -164,7 +164,6 @@ __device__ __forceinline__ void softmax_rows(const FwdParams& p, FwdCtl<FwdCfg<D
     for (int c = 0; c < 4; ++c) {
       uint32_t r[32];
       tmem_ld32(tS + c * 32, r);
-      tmem_wait_ld();
       if (mixed) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) imax = max(imax, ((mw[c] >> i) & 1u) ? INT_MIN : static_cast<int>(r[i]));
@@ -183,7 +182,6 @@ __device__ __forceinline__ void softmax_rows(const FwdParams& p, FwdCtl<FwdCfg<D
     for (int c = 0; c < 4; ++c) {
       uint32_t r[32];
       tmem_ld32(tS + c * 32, r);
-      tmem_wait_ld();
       uint32_t packed[8];
 #pragma unroll
       for (int g = 0; g < 8; ++g) {
@@ -222,7 +220,6 @@ __device__ __forceinline__ void softmax_rows(const FwdParams& p, FwdCtl<FwdCfg<D
     for (int c = 0; c < D / 32; ++c) {
       uint32_t r[32];
       tmem_ld32(tO + c * 32, r);
-      tmem_wait_ld();
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         const float x = __uint_as_float(r[i] + kMagicBits);          // kMagic + O~neg, exact
@@ -308,6 +305,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     tma_prefetch_desc(&map_v);
   }
   if (warp == 0) {
+    __syncwarp();
     tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
     tmem_relinquish();
   }

@@ -1,0 +1,188 @@
+"""GPU parity tests of the forward pass proper, through the C ABI.
+
+Bar: int8 output within +-1 LSB of the quantised CPU oracle on >= 99.9 % of the elements and within
++-2 everywhere (tests/_util.py); the reference's own criterion (mean relative deviation from the
+fp32 golden < 20 %, inc/utils.hpp:59-89) is checked alongside."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from _util import GOLDEN, assert_parity, parity_stats, sample_rows
+
+pytestmark = [pytest.mark.gpu, pytest.mark.timeout(600)]
+
+
+@pytest.fixture(scope="module")
+def torch_dev():
+    import torch
+    assert torch.cuda.is_available()
+    torch.cuda.set_device(0)
+    return torch
+
+
+def _clean(pkg):
+    st, words = pkg.device_status()
+    assert st == pkg.OK, f"device status words {words}"
+
+
+def _run(pkg, torch, q8, k8, v8, mask, amax, canary=True):
+    """Forward pass on device copies of the numpy inputs; O sits between canary bytes."""
+    B, H, S, D = q8.shape
+    tq, tk, tv, tm = (torch.from_numpy(np.ascontiguousarray(x)).cuda() for x in (q8, k8, v8, mask))
+    n = q8.size
+    pad = 4096
+    buf = torch.full((n + 2 * pad,), 0x5A, dtype=torch.int8, device="cuda")
+    to = buf[pad:pad + n]
+    pkg.FMHAInferI8(None, pkg.FMHAParamI8(*amax, 1.0), pkg.AttnDataDescriptor(B, S, H, D), tq, tk, tv, tm, to, True)
+    _clean(pkg)
+    host = buf.cpu().numpy()
+    assert np.all(host[:pad] == 0x5A) and np.all(host[pad + n:] == 0x5A), "output written outside its buffer"
+    return host[pad:pad + n].reshape(B, H, S, D)
+
+
+def test_forward_golden_cases(pkg, oracle, torch_dev):
+    for path in GOLDEN:
+        g = np.load(path)
+        amax = [float(x) for x in g["ref_amax"]]
+        got = _run(pkg, torch_dev, g["ref_q8"], g["ref_k8"], g["ref_v8"], g["mask"], amax)
+        assert_parity(got, g["oracle_o8"], path)
+        assert oracle.mean_rel_deviation(got, g["ref_o_fp32"], amax[3]) < 20.0, path
+
+
+def _quantised_case(wl, oracle, w, seed, mask=None):
+    q, k, v, m = wl.make_fp32_np(w, seed)
+    if mask is not None:
+        m = mask
+    q8, qa = wl.quantize_np(q)
+    k8, ka = wl.quantize_np(k)
+    v8, va = wl.quantize_np(v)
+    o, _ = oracle.fp32_attention(q, k, v, m)
+    oa = float(np.abs(o).max())
+    return q8, k8, v8, m, [qa, ka, va, oa], o
+
+
+@pytest.mark.parametrize("B,H,S,D", [(1, 2, 64, 64), (1, 1, 64, 128), (2, 2, 128, 64), (1, 3, 192, 128), (2, 1, 256, 128),
+                                     (1, 2, 320, 64), (1, 1, 448, 128), (3, 2, 512, 64), (1, 1, 1024, 128), (1, 2, 1088, 64)])
+def test_forward_shapes_no_padding(pkg, wl, oracle, torch_dev, B, H, S, D):
+    w = wl.Workload("t", B, H, S, D)
+    q8, k8, v8, m, amax, o = _quantised_case(wl, oracle, w, seed=S + D)
+    got = _run(pkg, torch_dev, q8, k8, v8, m, amax)
+    assert_parity(got, oracle.q128(q8, k8, v8, m, amax), f"B{B}H{H}S{S}D{D}")
+    assert oracle.mean_rel_deviation(got, o, amax[3]) < 20.0
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_forward_valid_length_and_random_masks(pkg, wl, oracle, torch_dev, D):
+    B, H, S = 4, 2, 384
+    w = wl.Workload("t", B, H, S, D)
+    rng = np.random.default_rng(D)
+    valid = np.array([64, 192, 320, 384])
+    masks = {
+        "valid": wl.mask_from_valid(valid, S),
+        "bernoulli20": (rng.random((B, S)) < 0.2).astype(np.int8),          # the reference test's mask
+        "nonbinary": ((rng.random((B, S)) < 0.3) * rng.integers(1, 127, (B, S))).astype(np.int8),
+        "hole": np.concatenate([np.zeros((B, 128)), np.ones((B, 128)), np.zeros((B, 128))], 1).astype(np.int8),
+    }
+    for name, m in masks.items():
+        q8, k8, v8, m, amax, o = _quantised_case(wl, oracle, w, seed=3, mask=m)
+        got = _run(pkg, torch_dev, q8, k8, v8, m, amax)
+        assert_parity(got, oracle.q128(q8, k8, v8, (m != 0).astype(np.int8), amax), name)
+
+
+def test_fully_masked_batch_gives_zeros(pkg, wl, oracle, torch_dev):
+    w = wl.Workload("t", 2, 2, 128, 64)
+    m = np.zeros((2, 128), np.int8)
+    m[1] = 1
+    q8, k8, v8, m, amax, _ = _quantised_case(wl, oracle, w, seed=9, mask=m)
+    got = _run(pkg, torch_dev, q8, k8, v8, m, amax)
+    assert np.all(got[1] == 0)
+    assert_parity(got, oracle.q128(q8, k8, v8, m, amax), "fully masked batch")
+
+
+def test_saturating_output_range(pkg, wl, oracle, torch_dev):
+    """o_amax far too small: every output clamps to +-127 exactly like the oracle."""
+    w = wl.Workload("t", 1, 1, 128, 64)
+    q8, k8, v8, m, amax, _ = _quantised_case(wl, oracle, w, seed=4)
+    amax[3] *= 0.05
+    got = _run(pkg, torch_dev, q8, k8, v8, m, amax)
+    assert got.max() == 127 and got.min() == -127
+    assert_parity(got, oracle.q128(q8, k8, v8, m, amax), "saturation")
+
+
+def test_slice_entry_point_equals_whole(pkg, wl, oracle, torch_dev):
+    torch = torch_dev
+    B, H, S, D = 3, 4, 192, 64
+    w = wl.Workload("t", B, H, S, D, valid_choices=(64, 128, 192))
+    q8, k8, v8, m, amax, _ = _quantised_case(wl, oracle, w, seed=21)
+    whole = _run(pkg, torch, q8, k8, v8, m, amax)
+    tm = torch.from_numpy(m).cuda()
+    param, desc = pkg.FMHAParamI8(*amax, 1.0), pkg.AttnDataDescriptor(B, S, H, D)
+    parts = []
+    for begin, count in ((0, 5), (5, 3), (8, 4)):     # slices cut across batch boundaries
+        sl = slice(begin, begin + count)
+        tq, tk, tv = (torch.from_numpy(np.ascontiguousarray(x.reshape(B * H, S, D)[sl])).cuda() for x in (q8, k8, v8))
+        to = torch.zeros_like(tq)
+        pkg.FMHAInferI8Slice(None, param, desc, tq, tk, tv, tm, to, begin, count)
+        _clean(pkg)
+        parts.append(to.cpu().numpy())
+    assert np.array_equal(np.concatenate(parts).reshape(B, H, S, D), whole)
+
+
+def test_host_buffer_entry_point(pkg, wl, oracle, torch_dev):
+    torch = torch_dev
+    B, H, S, D = 2, 2, 256, 128
+    w = wl.Workload("t", B, H, S, D, valid_choices=(192, 256))
+    q8, k8, v8, m, amax, _ = _quantised_case(wl, oracle, w, seed=31)
+    dev = _run(pkg, torch, q8, k8, v8, m, amax)
+    hq, hk, hv, hm = (torch.from_numpy(x).pin_memory() for x in (q8, k8, v8, m))
+    ho = torch.zeros_like(hq).pin_memory()
+    pkg.FMHAInferI8Host(pkg.FMHAParamI8(*amax, 1.0), pkg.AttnDataDescriptor(B, S, H, D), hq, hk, hv, hm, ho)
+    assert np.array_equal(ho.numpy(), dev)
+    ho2 = np.zeros_like(q8)                     # pageable memory works too
+    pkg.FMHAInferI8Host(pkg.FMHAParamI8(*amax, 1.0), pkg.AttnDataDescriptor(B, S, H, D), q8, k8, v8, m, ho2)
+    assert np.array_equal(ho2, dev)
+
+
+def test_repeatable_and_stream_ordered(pkg, wl, oracle, torch_dev):
+    torch = torch_dev
+    w = wl.Workload("t", 2, 2, 256, 64)
+    q8, k8, v8, m, amax, _ = _quantised_case(wl, oracle, w, seed=41)
+    a = _run(pkg, torch, q8, k8, v8, m, amax)
+    s = torch.cuda.Stream()
+    tq, tk, tv, tm = (torch.from_numpy(x).cuda() for x in (q8, k8, v8, m))
+    to = torch.zeros_like(tq)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s):
+        for _ in range(3):
+            pkg.FMHAInferI8(s, pkg.FMHAParamI8(*amax, 1.0), pkg.AttnDataDescriptor(2, 256, 2, 64), tq, tk, tv, tm, to, True)
+    s.synchronize()
+    _clean(pkg)
+    assert np.array_equal(to.cpu().numpy(), a)
+
+
+def test_cpp_entry_point(pkg, wl, oracle, torch_dev):
+    """gpuImpl::FMHAInferI8 itself (structs by value), as a caller of the reference would invoke it."""
+    torch = torch_dev
+
+    class Param(ctypes.Structure):
+        _fields_ = [(n, ctypes.c_float) for n in ("q_amax", "k_amax", "v_amax", "o_amax", "s_max")]
+
+    class Desc(ctypes.Structure):
+        _fields_ = [(n, ctypes.c_int) for n in ("batch_num", "seq_len", "head_num", "head_dim")]
+
+    L = ctypes.CDLL(pkg.LIB_PATH)
+    fn = getattr(L, "_ZN7gpuImpl11FMHAInferI8EP11CUstream_st11FMHAParamI818AttnDataDescriptorPKvS5_S5_S5_Pvb")
+    fn.argtypes = [ctypes.c_void_p, Param, Desc] + [ctypes.c_void_p] * 5 + [ctypes.c_bool]
+    fn.restype = None
+    w = wl.Workload("t", 1, 2, 128, 64)
+    q8, k8, v8, m, amax, _ = _quantised_case(wl, oracle, w, seed=51)
+    want = _run(pkg, torch, q8, k8, v8, m, amax)
+    tq, tk, tv, tm = (torch.from_numpy(x).cuda() for x in (q8, k8, v8, m))
+    to = torch.zeros_like(tq)
+    torch.cuda.synchronize()
+    fn(None, Param(*amax, 1.0), Desc(1, 128, 2, 64), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), tm.data_ptr(), to.data_ptr(), True)
+    torch.cuda.synchronize()
+    assert np.array_equal(to.cpu().numpy(), want)
+    fn(None, Param(*amax, 1.0), Desc(1, 128, 2, 64), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), tm.data_ptr(), to.data_ptr(), False)
+    assert L.fmha_i8_sm100_last_status() == pkg.ERR_NO_CUDA_CORE_PATH
