@@ -63,7 +63,7 @@ DeviceInfo* current_device(int* err) {
 }
 
 template <int D> size_t fwd_smem_bytes() {
-  return 1024 + FwdCfg<D>::kTilesBytesTotal + sizeof(FwdCtl<FwdCfg<D>::kStages>);
+  return 1024 + FwdCfg<D>::kTilesBytesTotal + 2 * kBiasBytes + sizeof(FwdCtl<FwdCfg<D>::kStages>);
 }
 template <int D> size_t qk_smem_bytes() { return 1024 + 2 * kTile * D + sizeof(DebugCtl); }
 template <int D> size_t pv_smem_bytes() { return 1024 + kTile * D + kTile * kTile + sizeof(DebugCtl); }
@@ -148,13 +148,8 @@ int fill_params(FwdParams* p, const float amax[5], const int desc[4]) {
   p->row_scale = reference_row_scale(desc[3]);
   p->scale_qk = amax[0] * amax[1] / (127.f * 127.f);
   p->scale_v_out = amax[2] * (1.0f / (amax[3] * 128.f));
-  const float c2 = static_cast<float>(static_cast<double>(p->row_scale) * static_cast<double>(p->scale_qk) * 1.4426950408889634);
-  uint32_t bits;
-  std::memcpy(&bits, &c2, 4);
-  bits &= 0xFFFFFFFCu;
-  std::memcpy(&p->c2, &bits, 4);
-  p->c2_bias = static_cast<float>(static_cast<double>(kMagic) * static_cast<double>(p->c2));
-  if (!(p->c2 > 0.f) || !std::isfinite(p->c2_bias)) return FMHA_I8_ERR_BAD_AMAX;
+  p->c2 = static_cast<float>(static_cast<double>(p->row_scale) * static_cast<double>(p->scale_qk) * 1.4426950408889634);
+  if (!(p->c2 > 0.f) || !std::isfinite(p->c2 * kMagic)) return FMHA_I8_ERR_BAD_AMAX;
   return FMHA_I8_OK;
 }
 

@@ -6,21 +6,29 @@
 //
 //   work unit  = (batch*head, pair of 128-row query tiles); one CTA per unit, one CTA per SM
 //   warp 8     = loader: TMA brings Q (once) and a ring of K and V tiles into swizzled shared memory
-//   warp 9     = MMA issuer: one thread issues tcgen05.mma kind::i8
-//                  S_w   = Q_w . K_j^T        (smem x smem  -> int32 in tensor memory)
-//                  O~_w  = P_w . V_j          (tmem x smem  -> int32 in tensor memory)
+//   warp 9     = MMA issuer: one thread issues tcgen05.mma
+//                  S_w   = bias + Q_w . K_j^T   (smem x smem  -> int32 in tensor memory)
+//                  O~_w  = bias + P_w . V_j     (tmem x smem  -> int32 in tensor memory)
 //   warps 0-3  = softmax group of query tile 0, warps 4-7 = of query tile 1: one thread owns one
 //                query row, so row max / row sum need no shuffles.  Per key tile a thread reads its S
 //                row from tensor memory twice (integer max, then exp + requantise), writes the 8-bit P
-//                row back over the front of S, and after P.V drains the int32 partial output into its
-//                fp32 running row.
+//                row back over the front of S, and after P.V drains the partial output into its fp32
+//                running row.
+//   warps 10-11 idle (they complete the third warpgroup so registers can be moved to the softmax
+//                groups with setmaxnreg).
+//
+// The bias: every accumulator is first written by a one-step fp16 MMA whose operands hold 4096 and
+// 3072, i.e. the fp32 value 1.5*2^23 (bits 0x4B400000); the int8 MMAs then add their integer result
+// to that bit pattern.  Read back as a float the accumulator is exactly 1.5*2^23 + s, so the
+// softmax threads never convert integers to floats: one fused multiply-add turns the raw
+// accumulator into the exponent argument (or into the rescaled partial output).
 //
 // Tensor memory (512 columns x 128 lanes x 32 bit): S_0 [0,128) S_1 [128,256) O~_0 [256,256+D)
 // O~_1 [256+D,256+2D).  P_w occupies the first 32 columns of S_w (four int8 per column).
 //
 // Numerics kept equal to the reference kernel within the test tolerance: the running output is kept
 // unnormalised (divided by the row sum once at the end) instead of renormalised after every tile,
-// exp() is ex2.approx on an argument formed exactly in the integer domain, and masked keys
+// exp() is ex2.approx on an argument formed exactly from the integer accumulator, and masked keys
 // contribute exactly zero (the reference adds a large negative number before scaling,
 // inc/fmha_i8.cuh:191-193).  Key tiles with no unmasked key are skipped.
 #pragma once
@@ -35,12 +43,15 @@ namespace fmha {
 constexpr int kTile = 128;           // query rows per tile == keys per tile
 constexpr int kMaxSeq = 32768;
 constexpr int kMaxTiles = kMaxSeq / kTile;
-constexpr int kFwdThreads = 320;
+constexpr int kFwdThreads = 384;     // three warpgroups
 constexpr int kWarpLoad = 8;
 constexpr int kWarpMma = 9;
+constexpr int kRegsSoftmax = 232;    // 8 warps x 232 + 4 warps x 40 = 2016 <= 2048 warp-registers
+constexpr int kRegsOther = 40;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kMagic = 12582912.0f;          // 1.5 * 2^23: float whose ulp is 1 over [2^23, 2^24)
 constexpr uint32_t kMagicBits = 0x4B400000u;
+constexpr int kBiasBytes = 4096;               // 128 rows x 16 fp16, unswizzled core-matrix layout
 
 template <int D> struct FwdCfg {
   static_assert(D == 64 || D == 128, "head_dim must be 64 or 128");
@@ -56,8 +67,7 @@ struct FwdParams {
   float row_scale;      // 1/sqrt(D), the reference's constant (inc/fmha_i8.cuh:71)
   float scale_qk;       // q_amax*k_amax/127^2 (inc/fmha_i8.cuh:72)
   float scale_v_out;    // v_amax/(o_amax*128) (inc/fmha_i8.cuh:318)
-  float c2;             // row_scale*scale_qk*log2(e) with the two lowest mantissa bits cleared
-  float c2_bias;        // kMagic*c2, exact because c2 has 22 significant bits
+  float c2;             // row_scale*scale_qk*log2(e)
   unsigned* status;     // eight device status words
 };
 
@@ -125,8 +135,147 @@ __device__ void scan_mask(Ctl* ctl, const int8_t* mask_row, int S, int n_tiles) 
   }
 }
 
-// One softmax thread: query row `row` of query tile w.  Returns false if a wait gave up.
-template <int D, bool kDummy = false>
+// Writes the two constant fp16 operands of the bias MMA: A[m][0] = 4096, B[n][0] = 3072, all other
+// elements zero, in the unswizzled K-major layout (core matrix = 8 rows x 16 bytes, the two K halves
+// of a row group 128 bytes apart, row groups 256 bytes apart).
+__device__ __forceinline__ void fill_bias_operands(uint8_t* bias_a, uint8_t* bias_b) {
+  for (int i = threadIdx.x; i < 2 * kBiasBytes / 16; i += blockDim.x)
+    reinterpret_cast<uint4*>(bias_a)[i] = make_uint4(0u, 0u, 0u, 0u);   // bias_b follows bias_a
+  __syncthreads();
+  if (threadIdx.x < kTile) {
+    const int m = threadIdx.x;
+    const int off = (m >> 3) * 256 + (m & 7) * 16;
+    *reinterpret_cast<uint16_t*>(bias_a + off) = 0x6C00u;   // 4096.0 in fp16
+    *reinterpret_cast<uint16_t*>(bias_b + off) = 0x6A00u;   // 3072.0 in fp16
+  }
+  fence_proxy_async_smem();
+}
+
+struct TileStats {
+  float m_tile;   // row maximum of the scaled scores of this tile (the reference's thread_max)
+  float l_tile;   // row sum of exp(score - m_tile) (the reference's thread_sum)
+};
+
+// Row maximum over 32 raw accumulator words (biased integers compare like the integers themselves).
+template <bool kMixed>
+__device__ __forceinline__ int chunk_max(const uint32_t (&r)[32], uint32_t mw, int imax) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    int a = static_cast<int>(r[i]), b = static_cast<int>(r[i + 1]);
+    if (kMixed) {
+      if ((mw >> i) & 1u) a = INT_MIN;
+      if ((mw >> (i + 1)) & 1u) b = INT_MIN;
+    }
+    imax = max(imax, max(a, b));
+  }
+  return imax;
+}
+
+// 32 scores -> 32 probabilities (summed into sum_a/sum_b) -> eight words of packed signed bytes
+// holding -rn(128 p).  x = raw accumulator read as float = kMagic + s.
+template <bool kMixed>
+__device__ __forceinline__ void chunk_exp_pack(const uint32_t (&r)[32], uint32_t mw, const float2 c2, const float2 neg_hi,
+                                               const float2 neg_128f, float2& sum_a, float2& sum_b, uint32_t (&packed)[8]) {
+  const float2 magic2 = make_float2(kMagic, kMagic);
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    float2 x01 = make_float2(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]));
+    float2 x23 = make_float2(__uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
+    if (kMixed) {
+      if ((mw >> (4 * g)) & 1u) x01.x = -INFINITY;
+      if ((mw >> (4 * g + 1)) & 1u) x01.y = -INFINITY;
+      if ((mw >> (4 * g + 2)) & 1u) x23.x = -INFINITY;
+      if ((mw >> (4 * g + 3)) & 1u) x23.y = -INFINITY;
+    }
+    const float2 a01 = __ffma2_rn(x01, c2, neg_hi);
+    const float2 a23 = __ffma2_rn(x23, c2, neg_hi);
+    const float2 p01 = make_float2(ex2_approx(a01.x), ex2_approx(a01.y));
+    const float2 p23 = make_float2(ex2_approx(a23.x), ex2_approx(a23.y));
+    sum_a = __fadd2_rn(sum_a, p01);
+    sum_b = __fadd2_rn(sum_b, p23);
+    const float2 y01 = __ffma2_rn(p01, neg_128f, magic2);      // low byte = two's complement of -P8
+    const float2 y23 = __ffma2_rn(p23, neg_128f, magic2);
+    packed[g] = __byte_perm(__byte_perm(__float_as_uint(y01.x), __float_as_uint(y01.y), 0x0040),
+                            __byte_perm(__float_as_uint(y23.x), __float_as_uint(y23.y), 0x0040), 0x5410);
+  }
+}
+
+// S row (tensor memory) -> statistics + quantised P row (tensor memory, over the front of S).
+// Fast path: no masked key in the tile.  The four 32-column chunks are double-buffered so that a
+// tensor-memory load is always in flight while the previous chunk is processed.
+__device__ __forceinline__ TileStats softmax_tile_fast(const uint32_t tS, const FwdParams& p) {
+  uint32_t ra[32], rb[32];
+  int imax = INT_MIN;
+  tmem_ld32_issue(tS, ra);
+  tmem_ld_fence(ra); tmem_ld32_issue(tS + 32, rb); imax = chunk_max<false>(ra, 0u, imax);
+  tmem_ld_fence(rb); tmem_ld32_issue(tS + 64, ra); imax = chunk_max<false>(rb, 0u, imax);
+  tmem_ld_fence(ra); tmem_ld32_issue(tS + 96, rb); imax = chunk_max<false>(ra, 0u, imax);
+  tmem_ld_fence(rb); tmem_ld32_issue(tS, ra);      imax = chunk_max<false>(rb, 0u, imax);
+
+  // exponent argument (s - smax) * c2 = x * c2 - M * c2 with x = kMagic + s and M = kMagic + smax.
+  // M * c2 = hi + lo exactly (lo is the rounding residual); the factor 2^-lo is folded into the
+  // quantisation constant and the row sum, so nothing is lost and nothing is paid per element.
+  const float M = __uint_as_float(static_cast<uint32_t>(imax));
+  const float hi = M * p.c2;
+  const float lo = fmaf(M, p.c2, -hi);
+  const float f = fmaf(-lo, 0.6931471805599453f, 1.0f);
+  const float2 c2 = make_float2(p.c2, p.c2), neg_hi = make_float2(-hi, -hi), neg_128f = make_float2(-128.f * f, -128.f * f);
+  float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+  uint32_t packed[8];
+  tmem_ld_fence(ra); tmem_ld32_issue(tS + 32, rb); chunk_exp_pack<false>(ra, 0u, c2, neg_hi, neg_128f, sum_a, sum_b, packed); tmem_st8(tS, packed);
+  tmem_ld_fence(rb); tmem_ld32_issue(tS + 64, ra); chunk_exp_pack<false>(rb, 0u, c2, neg_hi, neg_128f, sum_a, sum_b, packed); tmem_st8(tS + 8, packed);
+  tmem_ld_fence(ra); tmem_ld32_issue(tS + 96, rb); chunk_exp_pack<false>(ra, 0u, c2, neg_hi, neg_128f, sum_a, sum_b, packed); tmem_st8(tS + 16, packed);
+  tmem_ld_fence(rb);                               chunk_exp_pack<false>(rb, 0u, c2, neg_hi, neg_128f, sum_a, sum_b, packed); tmem_st8(tS + 24, packed);
+
+  TileStats st;
+  // the value the reference computes for the maximal element (inc/fmha_i8.cuh:196)
+  st.m_tile = (p.row_scale * static_cast<float>(imax - static_cast<int>(kMagicBits))) * p.scale_qk;
+  st.l_tile = f * ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
+  return st;
+}
+
+// Per-key path for tiles that contain masked keys: compact (rolled) code, used at most once per row
+// with valid-length padding.
+__device__ __forceinline__ TileStats softmax_tile_mixed(const uint32_t tS, const float c2s, const float row_scale,
+                                                     const float scale_qk, const uint32_t* mask_words) {
+  uint32_t r[32];
+  int imax = INT_MIN;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    tmem_ld32(tS + c * 32, r);
+    imax = chunk_max<true>(r, mask_words[c], imax);
+  }
+  const float M = __uint_as_float(static_cast<uint32_t>(imax));
+  const float hi = M * c2s;
+  const float lo = fmaf(M, c2s, -hi);
+  const float f = fmaf(-lo, 0.6931471805599453f, 1.0f);
+  const float2 c2 = make_float2(c2s, c2s), neg_hi = make_float2(-hi, -hi), neg_128f = make_float2(-128.f * f, -128.f * f);
+  float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t packed[8];
+    tmem_ld32(tS + c * 32, r);
+    chunk_exp_pack<true>(r, mask_words[c], c2, neg_hi, neg_128f, sum_a, sum_b, packed);
+    tmem_st8(tS + c * 8, packed);
+  }
+  TileStats st;
+  st.m_tile = (row_scale * static_cast<float>(imax - static_cast<int>(kMagicBits))) * scale_qk;
+  st.l_tile = f * ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
+  return st;
+}
+
+// o2 (+)= e_cur * (P8 . V) for 32 output columns; x = raw accumulator read as float = kMagic + O~neg.
+__device__ __forceinline__ void drain_chunk(const uint32_t (&r)[32], float2* o2, const float2 neg_ec, const float2 e_bias, const float2 e_old) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 x = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+    const float2 t = __ffma2_rn(x, neg_ec, e_bias);          // e_cur * (P8 . V), exact product before rounding
+    o2[i] = __ffma2_rn(o2[i], e_old, t);
+  }
+}
+
+// One softmax thread: query row q_row of query tile w.
+template <int D>
 __device__ __forceinline__ void softmax_rows(const FwdParams& p, FwdCtl<FwdCfg<D>::kStages>* ctl, const int w,
                                              const uint32_t tmem_base, const int q_row, const int bh_local) {
   const int warp = threadIdx.x >> 5;
@@ -138,93 +287,50 @@ __device__ __forceinline__ void softmax_rows(const FwdParams& p, FwdCtl<FwdCfg<D
   const int n_live = ctl->n_live;
   volatile int* abort_flag = &ctl->abort;
 
-  float o[D];
+  float2 o2[D / 2];
 #pragma unroll
-  for (int i = 0; i < D; ++i) o[i] = 0.f;
+  for (int i = 0; i < D / 2; ++i) o2[i] = make_float2(0.f, 0.f);
   float m_run = -INFINITY, l_run = 0.f;
   bool ok = true;
 
+#pragma unroll 1
   for (int j = 0; j < n_live; ++j) {
     const uint32_t ph = static_cast<uint32_t>(j & 1);
     ok = __all_sync(0xFFFFFFFFu, mbar_wait(bar_s, ph, abort_flag));
     if (!ok) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_S_READY, j); break; }
     tc_fence_after();
 
-    const bool mixed = ctl->mixed[j] != 0;
-    uint32_t mw[4] = {0u, 0u, 0u, 0u};
-    if (mixed) {
-      const int t = ctl->live[j];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) mw[c] = ctl->maskbits[4 * t + c];
-    }
-
-    // ---- pass 1: row maximum of the unmasked keys, in the integer domain (the scale is positive)
-    int imax = INT_MIN;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t r[32];
-      tmem_ld32(tS + c * 32, r);
-      if (mixed) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) imax = max(imax, ((mw[c] >> i) & 1u) ? INT_MIN : static_cast<int>(r[i]));
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) imax = max(imax, static_cast<int>(r[i]));
-      }
-    }
-    // the value the reference computes for the maximal element (inc/fmha_i8.cuh:196)
-    const float m_tile = (p.row_scale * static_cast<float>(imax)) * p.scale_qk;
-
-    // ---- pass 2: p = 2^((s - smax) * c2), row sum, P8 = rn(-128 p) as signed bytes, written over S
-    const uint32_t bias = kMagicBits - static_cast<uint32_t>(imax);   // float(bits) = kMagic + (s - smax), exact
-    float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t r[32];
-      tmem_ld32(tS + c * 32, r);
-      uint32_t packed[8];
-#pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        uint32_t y[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = 4 * g + e;
-          float x = __uint_as_float(r[i] + bias);
-          if (mixed && ((mw[c] >> i) & 1u)) x = -INFINITY;
-          const float pe = ex2_approx(fmaf(x, p.c2, -p.c2_bias));
-          if (e == 0) sum0 += pe; else if (e == 1) sum1 += pe; else if (e == 2) sum2 += pe; else sum3 += pe;
-          y[e] = __float_as_uint(fmaf(pe, -128.f, kMagic));          // low byte = two's complement of -P8
-        }
-        packed[g] = __byte_perm(__byte_perm(y[0], y[1], 0x0040), __byte_perm(y[2], y[3], 0x0040), 0x5410);
-      }
-      tmem_st8(tS + c * 8, packed);
-    }
+    TileStats st;
+    if (ctl->mixed[j] != 0) st = softmax_tile_mixed(tS, p.c2, p.row_scale, p.scale_qk, &ctl->maskbits[4 * ctl->live[j]]);
+    else st = softmax_tile_fast(tS, p);
     tmem_wait_st();
     tc_fence_before();
     mbar_arrive(bar_p);
-    const float l_tile = (sum0 + sum1) + (sum2 + sum3);
 
     // ---- merge of tile statistics (inc/fmha_i8.cuh:301-304)
-    const float m_new = fmaxf(m_run, m_tile);
+    const float m_new = fmaxf(m_run, st.m_tile);
     const float e_old = __expf(m_run - m_new);                       // 0 on the first tile (m_run = -inf)
-    const float e_cur = clear_low2(__expf(m_tile - m_new));          // 22 significant bits: kMagic*e_cur is exact
-    l_run = fmaf(e_old, l_run, e_cur * l_tile);
+    const float e_cur = clear_low2(__expf(st.m_tile - m_new));       // 22 significant bits: kMagic*e_cur is exact
+    l_run = fmaf(e_old, l_run, e_cur * st.l_tile);
     m_run = m_new;
-    const float e_bias = e_cur * kMagic;
+    const float2 neg_ec = make_float2(-e_cur, -e_cur), e_bias = make_float2(e_cur * kMagic, e_cur * kMagic);
+    const float2 e_old2 = make_float2(e_old, e_old);
 
-    // ---- drain O~ = -(P8 . V) into the fp32 running row
+    // ---- drain O~ = bias - (P8 . V) into the fp32 running row, double-buffered
     ok = __all_sync(0xFFFFFFFFu, mbar_wait(bar_o, ph, abort_flag));
     if (!ok) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_O_READY, j); break; }
     tc_fence_after();
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
-      uint32_t r[32];
-      tmem_ld32(tO + c * 32, r);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float x = __uint_as_float(r[i] + kMagicBits);          // kMagic + O~neg, exact
-        const float t = fmaf(x, -e_cur, e_bias);                     // e_cur * (P8 . V)
-        o[c * 32 + i] = fmaf(o[c * 32 + i], e_old, t);
+    {
+      uint32_t ra[32], rb[32];
+      tmem_ld32_issue(tO, ra);
+      if (D == 128) {
+        tmem_ld_fence(ra); tmem_ld32_issue(tO + 32, rb); drain_chunk(ra, o2, neg_ec, e_bias, e_old2);
+        tmem_ld_fence(rb); tmem_ld32_issue(tO + 64, ra); drain_chunk(rb, o2 + 16, neg_ec, e_bias, e_old2);
+        tmem_ld_fence(ra); tmem_ld32_issue(tO + 96, rb); drain_chunk(ra, o2 + 32, neg_ec, e_bias, e_old2);
+        tmem_ld_fence(rb);                               drain_chunk(rb, o2 + 48, neg_ec, e_bias, e_old2);
+      } else {
+        tmem_ld_fence(ra); tmem_ld32_issue(tO + 32, rb); drain_chunk(ra, o2, neg_ec, e_bias, e_old2);
+        tmem_ld_fence(rb);                               drain_chunk(rb, o2 + 16, neg_ec, e_bias, e_old2);
       }
     }
     tc_fence_before();
@@ -243,8 +349,10 @@ __device__ __forceinline__ void softmax_rows(const FwdParams& p, FwdCtl<FwdCfg<D
         uint32_t b4 = 0;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float f = p.scale_v_out * (o[c * 16 + g * 4 + e] * inv);
-          const int q8 = __float2int_rn(fmaxf(fminf(f, 127.f), -127.f));
+          const float2 v2 = o2[(c * 16 + g * 4 + e) >> 1];
+          const float val = (e & 1) ? v2.y : v2.x;
+          const float fq = p.scale_v_out * (val * inv);
+          const int q8 = __float2int_rn(fmaxf(fminf(fq, 127.f), -127.f));
           b4 |= (static_cast<uint32_t>(q8) & 0xFFu) << (8 * e);
         }
         wds[g] = b4;
@@ -264,7 +372,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   // tiles need 1024-byte alignment (swizzle atoms); the launch reserves the slack
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  Ctl* ctl = reinterpret_cast<Ctl*>(tiles + Cfg::kTilesBytesTotal);
+  uint8_t* bias_a = tiles + Cfg::kTilesBytesTotal;
+  uint8_t* bias_b = bias_a + kBiasBytes;
+  Ctl* ctl = reinterpret_cast<Ctl*>(bias_b + kBiasBytes);
   const uint32_t q_smem = smem_u32(tiles);
   const uint32_t k_smem = q_smem + 2 * Cfg::kTileBytes;
   const uint32_t v_smem = k_smem + NS * Cfg::kTileBytes;
@@ -309,6 +419,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
     tmem_relinquish();
   }
+  fill_bias_operands(bias_a, bias_b);
   scan_mask(ctl, p.mask + static_cast<int64_t>(batch) * p.S, p.S, n_tiles);
   tc_fence_before();
   __syncthreads();
@@ -319,91 +430,100 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (warp < 8) {
     // ------------------------------------------------------------------ softmax groups
+    setmaxnreg_inc<kRegsSoftmax>();
     const int w = warp >> 2;
     if (w < nq) {
       const int row_in_tile = (warp & 3) * 32 + lane;
       softmax_rows<D>(p, ctl, w, tmem_base, q_row0 + w * kTile + row_in_tile, bh_local);
     }
-  } else if (warp == kWarpLoad) {
-    // ------------------------------------------------------------------ loader
-    if (lane == 0 && n_live > 0) {
-      const uint32_t bar_q = smem_u32(&ctl->q_full);
-      mbar_arrive_expect_tx(bar_q, static_cast<uint32_t>(nq * Cfg::kTileBytes));
-      for (int w = 0; w < nq; ++w) tma_load_3d(q_smem + w * Cfg::kTileBytes, &map_q, bar_q, 0, q_row0 + w * kTile, bh_local);
-      bool ok = true;
-      for (int j = 0; j < n_live && ok; ++j) {
-        const int t = ctl->live[j];
-        const int s = j % NS, round = j / NS;
-        if (round > 0 && !mbar_wait(smem_u32(&ctl->k_empty[s]), static_cast<uint32_t>((round - 1) & 1), abort_flag)) {
-          raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_FREE, j); ok = false; break;
-        }
-        mbar_arrive_expect_tx(smem_u32(&ctl->k_full[s]), Cfg::kTileBytes);
-        tma_load_3d(k_smem + s * Cfg::kTileBytes, &map_k, smem_u32(&ctl->k_full[s]), 0, t * kTile, bh_local);
-        if (round > 0 && !mbar_wait(smem_u32(&ctl->v_empty[s]), static_cast<uint32_t>((round - 1) & 1), abort_flag)) {
-          raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_V_FREE, j); ok = false; break;
-        }
-        mbar_arrive_expect_tx(smem_u32(&ctl->v_full[s]), Cfg::kTileBytes);
-        tma_load_3d(v_smem + s * Cfg::kTileBytes, &map_v, smem_u32(&ctl->v_full[s]), 0, t * kTile, bh_local);
-      }
-      if (!ok) {
-        // unwinding: let copies that are still in flight land before the CTA may exit
-        const long long t0 = clock64();
-        while (clock64() - t0 < 2000000LL) { /* about a millisecond */ }
-      }
-    }
   } else {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && n_live > 0) {
-      constexpr uint32_t idesc_s = make_idesc_i8(kTile, false);   // S = Q.K^T : N = 128 keys, both K-major
-      constexpr uint32_t idesc_o = make_idesc_i8(D, true);        // O = P.V   : N = D, V is MN-major
-      bool ok = true;
-      auto issue_s = [&](int w, int stage) {
-        const uint64_t dq = make_smem_desc(q_smem + w * Cfg::kTileBytes, D);
-        const uint64_t dk = make_smem_desc(k_smem + stage * Cfg::kTileBytes, D);
-#pragma unroll
-        for (int kk = 0; kk < D / 32; ++kk)
-          mma_i8_ss(tmem_base + w * kTile, desc_advance(dq, kk * 32), desc_advance(dk, kk * 32), idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(smem_u32(&ctl->s_full[w]));
-      };
-      auto issue_o = [&](int w, int stage) {
-        const uint64_t dv = make_smem_desc(v_smem + stage * Cfg::kTileBytes, D);
-#pragma unroll
-        for (int kk = 0; kk < kTile / 32; ++kk)
-          mma_i8_ts(tmem_base + 2 * kTile + w * D, tmem_base + w * kTile + kk * 8, desc_advance(dv, kk * 32 * D), idesc_o,
-                    kk > 0 ? 1u : 0u);
-        mma_commit(smem_u32(&ctl->o_full[w]));
-      };
-      do {
-        if (!mbar_wait(smem_u32(&ctl->q_full), 0u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_Q_LOAD, 0); ok = false; break; }
-        if (!mbar_wait(smem_u32(&ctl->k_full[0]), 0u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_LOAD, 0); ok = false; break; }
-        tc_fence_after();
-        for (int w = 0; w < nq; ++w) issue_s(w, 0);
-        mma_commit(smem_u32(&ctl->k_empty[0]));
+    setmaxnreg_dec<kRegsOther>();
+    if (warp == kWarpLoad) {
+      // ---------------------------------------------------------------- loader
+      if (lane == 0 && n_live > 0) {
+        const uint32_t bar_q = smem_u32(&ctl->q_full);
+        mbar_arrive_expect_tx(bar_q, static_cast<uint32_t>(nq * Cfg::kTileBytes));
+        for (int w = 0; w < nq; ++w) tma_load_3d(q_smem + w * Cfg::kTileBytes, &map_q, bar_q, 0, q_row0 + w * kTile, bh_local);
+        bool ok = true;
         for (int j = 0; j < n_live && ok; ++j) {
-          const int s = j % NS;
-          const uint32_t ph = static_cast<uint32_t>(j & 1);
-          if (!mbar_wait(smem_u32(&ctl->v_full[s]), static_cast<uint32_t>((j / NS) & 1), abort_flag)) {
-            raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_V_LOAD, j); ok = false; break;
+          const int t = ctl->live[j];
+          const int s = j % NS, round = j / NS;
+          if (round > 0 && !mbar_wait(smem_u32(&ctl->k_empty[s]), static_cast<uint32_t>((round - 1) & 1), abort_flag)) {
+            raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_FREE, j); ok = false; break;
           }
-          const int jn = j + 1, sn = jn % NS;
-          for (int w = 0; w < nq; ++w) {
-            if (!mbar_wait(smem_u32(&ctl->p_ready[w]), ph, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_P_READY, j); ok = false; break; }
-            if (j > 0 && !mbar_wait(smem_u32(&ctl->o_free[w]), ph ^ 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_O_FREE, j); ok = false; break; }
-            tc_fence_after();
-            issue_o(w, s);
-            if (w == nq - 1) mma_commit(smem_u32(&ctl->v_empty[s]));
-            if (jn < n_live) {
-              if (w == 0 && !mbar_wait(smem_u32(&ctl->k_full[sn]), static_cast<uint32_t>((jn / NS) & 1), abort_flag)) {
-                raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_LOAD, jn); ok = false; break;
-              }
+          mbar_arrive_expect_tx(smem_u32(&ctl->k_full[s]), Cfg::kTileBytes);
+          tma_load_3d(k_smem + s * Cfg::kTileBytes, &map_k, smem_u32(&ctl->k_full[s]), 0, t * kTile, bh_local);
+          if (round > 0 && !mbar_wait(smem_u32(&ctl->v_empty[s]), static_cast<uint32_t>((round - 1) & 1), abort_flag)) {
+            raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_V_FREE, j); ok = false; break;
+          }
+          mbar_arrive_expect_tx(smem_u32(&ctl->v_full[s]), Cfg::kTileBytes);
+          tma_load_3d(v_smem + s * Cfg::kTileBytes, &map_v, smem_u32(&ctl->v_full[s]), 0, t * kTile, bh_local);
+        }
+        if (!ok) {
+          // unwinding: let copies that are still in flight land before the CTA may exit
+          const long long t0 = clock64();
+          while (clock64() - t0 < 2000000LL) { /* about a millisecond */ }
+        }
+      }
+    } else if (warp == kWarpMma) {
+      // ---------------------------------------------------------------- MMA issuer
+      if (lane == 0 && n_live > 0) {
+        constexpr uint32_t idesc_s = make_idesc_i8(kTile, false);   // S = Q.K^T : N = 128 keys, both K-major
+        constexpr uint32_t idesc_o = make_idesc_i8(D, true);        // O = P.V   : N = D, V is MN-major
+        constexpr uint32_t idesc_bias_s = make_idesc_f16(kTile);
+        constexpr uint32_t idesc_bias_o = make_idesc_f16(D);
+        const uint64_t d_bias_a = make_smem_desc_noswizzle(smem_u32(bias_a), 128, 256);
+        const uint64_t d_bias_b = make_smem_desc_noswizzle(smem_u32(bias_b), 128, 256);
+        bool ok = true;
+        auto issue_s = [&](int w, int stage) {
+          const uint64_t dq = make_smem_desc(q_smem + w * Cfg::kTileBytes, D);
+          const uint64_t dk = make_smem_desc(k_smem + stage * Cfg::kTileBytes, D);
+          mma_f16_ss(tmem_base + w * kTile, d_bias_a, d_bias_b, idesc_bias_s, 0u);      // accumulator := 0x4B400000
+#pragma unroll
+          for (int kk = 0; kk < D / 32; ++kk)
+            mma_i8_ss(tmem_base + w * kTile, desc_advance(dq, kk * 32), desc_advance(dk, kk * 32), idesc_s, 1u);
+          mma_commit(smem_u32(&ctl->s_full[w]));
+        };
+        auto issue_o = [&](int w, int stage) {
+          const uint64_t dv = make_smem_desc(v_smem + stage * Cfg::kTileBytes, D);
+          mma_f16_ss(tmem_base + 2 * kTile + w * D, d_bias_a, d_bias_b, idesc_bias_o, 0u);
+#pragma unroll
+          for (int kk = 0; kk < kTile / 32; ++kk)
+            mma_i8_ts(tmem_base + 2 * kTile + w * D, tmem_base + w * kTile + kk * 8, desc_advance(dv, kk * 32 * D), idesc_o, 1u);
+          mma_commit(smem_u32(&ctl->o_full[w]));
+        };
+        do {
+          if (!mbar_wait(smem_u32(&ctl->q_full), 0u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_Q_LOAD, 0); ok = false; break; }
+          if (!mbar_wait(smem_u32(&ctl->k_full[0]), 0u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_LOAD, 0); ok = false; break; }
+          tc_fence_after();
+          for (int w = 0; w < nq; ++w) issue_s(w, 0);
+          mma_commit(smem_u32(&ctl->k_empty[0]));
+          for (int j = 0; j < n_live && ok; ++j) {
+            const int s = j % NS;
+            const uint32_t ph = static_cast<uint32_t>(j & 1);
+            if (!mbar_wait(smem_u32(&ctl->v_full[s]), static_cast<uint32_t>((j / NS) & 1), abort_flag)) {
+              raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_V_LOAD, j); ok = false; break;
+            }
+            const int jn = j + 1, sn = jn % NS;
+            for (int w = 0; w < nq; ++w) {
+              if (!mbar_wait(smem_u32(&ctl->p_ready[w]), ph, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_P_READY, j); ok = false; break; }
+              if (j > 0 && !mbar_wait(smem_u32(&ctl->o_free[w]), ph ^ 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_O_FREE, j); ok = false; break; }
               tc_fence_after();
-              // S_w / P_w columns are free again: the tensor pipe runs this thread's MMAs in order
-              issue_s(w, sn);
-              if (w == nq - 1) mma_commit(smem_u32(&ctl->k_empty[sn]));
+              issue_o(w, s);
+              if (w == nq - 1) mma_commit(smem_u32(&ctl->v_empty[s]));
+              if (jn < n_live) {
+                if (w == 0 && !mbar_wait(smem_u32(&ctl->k_full[sn]), static_cast<uint32_t>((jn / NS) & 1), abort_flag)) {
+                  raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_LOAD, jn); ok = false; break;
+                }
+                tc_fence_after();
+                // S_w / P_w columns are free again: the tensor pipe runs this thread's MMAs in order
+                issue_s(w, sn);
+                if (w == nq - 1) mma_commit(smem_u32(&ctl->k_empty[sn]));
+              }
             }
           }
-        }
-      } while (false);
+        } while (false);
+      }
     }
   }
 
