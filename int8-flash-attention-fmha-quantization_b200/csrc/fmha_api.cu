@@ -373,6 +373,14 @@ unsigned long long fmha_i8_sm100_launch_count(void) { return g_launch_count.load
 
 int fmha_i8_sm100_version(void) { return 100; }
 
+#ifdef FMHA_TRACE
+// Performance-work builds only: copies out the timeline stamps of the first CTA.
+int fmha_i8_sm100_read_trace(long long* out) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return FMHA_I8_ERR_LAUNCH;
+  return cudaMemcpyFromSymbol(out, fmha::g_trace, sizeof(long long) * 16 * 512) == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH;
+}
+#endif
+
 }  // extern "C"
 
 // The reference project's C++ entry point (inc/fmha_i8.h:5-17), kept symbol-for-symbol.

@@ -40,14 +40,26 @@
 
 namespace fmha {
 
+// Optional timeline tracing for performance work: with -DFMHA_TRACE the first CTA records clock64()
+// stamps of its phase boundaries.  Compiled out of the product build.
+#ifndef FMHA_TRACE_Q
+#define FMHA_TRACE_Q 0
+#endif
+#ifdef FMHA_TRACE
+__device__ long long g_trace[16][512];
+#define FMHA_STAMP(slot, idx) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (idx) < 512) g_trace[slot][idx] = clock64(); } while (0)
+#else
+#define FMHA_STAMP(slot, idx) do { } while (0)
+#endif
+
 constexpr int kTile = 128;           // query rows per tile == keys per tile
 constexpr int kMaxSeq = 32768;
 constexpr int kMaxTiles = kMaxSeq / kTile;
 constexpr int kFwdThreads = 384;     // three warpgroups
 constexpr int kWarpLoad = 8;
 constexpr int kWarpMma = 9;
-constexpr int kRegsSoftmax = 232;    // 8 warps x 232 + 4 warps x 40 = 2016 <= 2048 warp-registers
-constexpr int kRegsOther = 40;
+constexpr int kRegsSoftmax = 224;    // 8 warps x 224 + 4 warps x 56 = 2016 <= 2048 warp-registers
+constexpr int kRegsOther = 56;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kMagic = 12582912.0f;          // 1.5 * 2^23: float whose ulp is 1 over [2^23, 2^24)
 constexpr uint32_t kMagicBits = 0x4B400000u;
@@ -156,29 +168,31 @@ struct TileStats {
   float l_tile;   // row sum of exp(score - m_tile) (the reference's thread_sum)
 };
 
-// Row maximum over 32 raw accumulator words (biased integers compare like the integers themselves).
-template <bool kMixed>
-__device__ __forceinline__ int chunk_max(const uint32_t (&r)[32], uint32_t mw, int imax) {
+// Row maximum over N raw accumulator words (biased integers compare like the integers themselves).
+template <bool kMixed, int N>
+__device__ __forceinline__ void chunk_max(const uint32_t (&r)[N], uint32_t mw, int& max_a, int& max_b) {
 #pragma unroll
-  for (int i = 0; i < 32; i += 2) {
-    int a = static_cast<int>(r[i]), b = static_cast<int>(r[i + 1]);
+  for (int i = 0; i < N; i += 4) {
+    int a = static_cast<int>(r[i]), b = static_cast<int>(r[i + 1]), c = static_cast<int>(r[i + 2]), d = static_cast<int>(r[i + 3]);
     if (kMixed) {
       if ((mw >> i) & 1u) a = INT_MIN;
       if ((mw >> (i + 1)) & 1u) b = INT_MIN;
+      if ((mw >> (i + 2)) & 1u) c = INT_MIN;
+      if ((mw >> (i + 3)) & 1u) d = INT_MIN;
     }
-    imax = max(imax, max(a, b));
+    max_a = max(max_a, max(a, b));
+    max_b = max(max_b, max(c, d));
   }
-  return imax;
 }
 
-// 32 scores -> 32 probabilities (summed into sum_a/sum_b) -> eight words of packed signed bytes
-// holding -rn(128 p).  x = raw accumulator read as float = kMagic + s.
-template <bool kMixed>
-__device__ __forceinline__ void chunk_exp_pack(const uint32_t (&r)[32], uint32_t mw, const float2 c2, const float2 neg_hi,
-                                               const float2 neg_128f, float2& sum_a, float2& sum_b, uint32_t (&packed)[8]) {
+// N scores -> N probabilities (summed into four independent packed accumulators) -> N/4 words of
+// packed signed bytes holding -rn(128 p).  x = raw accumulator read as float = kMagic + s.
+template <bool kMixed, int N>
+__device__ __forceinline__ void chunk_exp_pack(const uint32_t (&r)[N], uint32_t mw, const float2 c2, const float2 neg_hi,
+                                               const float2 neg_128f, float2 (&sum)[4], uint32_t (&packed)[N / 4]) {
   const float2 magic2 = make_float2(kMagic, kMagic);
 #pragma unroll
-  for (int g = 0; g < 8; ++g) {
+  for (int g = 0; g < N / 4; ++g) {
     float2 x01 = make_float2(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]));
     float2 x23 = make_float2(__uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
     if (kMixed) {
@@ -191,8 +205,8 @@ __device__ __forceinline__ void chunk_exp_pack(const uint32_t (&r)[32], uint32_t
     const float2 a23 = __ffma2_rn(x23, c2, neg_hi);
     const float2 p01 = make_float2(ex2_approx(a01.x), ex2_approx(a01.y));
     const float2 p23 = make_float2(ex2_approx(a23.x), ex2_approx(a23.y));
-    sum_a = __fadd2_rn(sum_a, p01);
-    sum_b = __fadd2_rn(sum_b, p23);
+    sum[(2 * g) & 3] = __fadd2_rn(sum[(2 * g) & 3], p01);
+    sum[(2 * g + 1) & 3] = __fadd2_rn(sum[(2 * g + 1) & 3], p23);
     const float2 y01 = __ffma2_rn(p01, neg_128f, magic2);      // low byte = two's complement of -P8
     const float2 y23 = __ffma2_rn(p23, neg_128f, magic2);
     packed[g] = __byte_perm(__byte_perm(__float_as_uint(y01.x), __float_as_uint(y01.y), 0x0040),
@@ -200,74 +214,159 @@ __device__ __forceinline__ void chunk_exp_pack(const uint32_t (&r)[32], uint32_t
   }
 }
 
-// S row (tensor memory) -> statistics + quantised P row (tensor memory, over the front of S).
-// Fast path: no masked key in the tile.  The four 32-column chunks are double-buffered so that a
-// tensor-memory load is always in flight while the previous chunk is processed.
-__device__ __forceinline__ TileStats softmax_tile_fast(const uint32_t tS, const FwdParams& p) {
-  uint32_t ra[32], rb[32];
-  int imax = INT_MIN;
-  tmem_ld32_issue(tS, ra);
-  tmem_ld_fence(ra); tmem_ld32_issue(tS + 32, rb); imax = chunk_max<false>(ra, 0u, imax);
-  tmem_ld_fence(rb); tmem_ld32_issue(tS + 64, ra); imax = chunk_max<false>(rb, 0u, imax);
-  tmem_ld_fence(ra); tmem_ld32_issue(tS + 96, rb); imax = chunk_max<false>(ra, 0u, imax);
-  tmem_ld_fence(rb); tmem_ld32_issue(tS, ra);      imax = chunk_max<false>(rb, 0u, imax);
+// The same work split in two stages so that the exponentials of the next chunk (XU pipe, one warp
+// instruction per 8 cycles) are interleaved IN PROGRAM ORDER with the packing of the current chunk
+// (FMA/ALU pipes): a warp issues in order, so a run of back-to-back MUFUs would leave the other
+// pipes idle.  chunk_exp alone is used for the first chunk, chunk_pack alone for the last.
+template <int N>
+__device__ __forceinline__ void chunk_exp(const uint32_t (&r)[N], const float2 c2, const float2 neg_hi, float2 (&pr)[N / 2]) {
+#pragma unroll
+  for (int i = 0; i < N / 2; ++i) {
+    const float2 x = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+    const float2 a = __ffma2_rn(x, c2, neg_hi);
+    pr[i] = make_float2(ex2_approx(a.x), ex2_approx(a.y));
+  }
+}
+__device__ __forceinline__ uint32_t pack_group(const float2 p01, const float2 p23, const float2 neg_128f, float2& sum_a, float2& sum_b) {
+  const float2 magic2 = make_float2(kMagic, kMagic);
+  sum_a = __fadd2_rn(sum_a, p01);
+  sum_b = __fadd2_rn(sum_b, p23);
+  const float2 y01 = __ffma2_rn(p01, neg_128f, magic2);      // low byte = two's complement of -P8
+  const float2 y23 = __ffma2_rn(p23, neg_128f, magic2);
+  return __byte_perm(__byte_perm(__float_as_uint(y01.x), __float_as_uint(y01.y), 0x0040),
+                     __byte_perm(__float_as_uint(y23.x), __float_as_uint(y23.y), 0x0040), 0x5410);
+}
+template <int N>
+__device__ __forceinline__ void chunk_pack(const float2 (&pr)[N / 2], const float2 neg_128f, float2 (&sum)[4], uint32_t (&packed)[N / 4]) {
+#pragma unroll
+  for (int g = 0; g < N / 4; ++g) packed[g] = pack_group(pr[2 * g], pr[2 * g + 1], neg_128f, sum[(2 * g) & 3], sum[(2 * g + 1) & 3]);
+}
+// exp of chunk `rn` (-> pn) interleaved with pack of chunk `pc` (-> packed), four elements at a time.
+template <int N>
+__device__ __forceinline__ void chunk_exp_and_pack(const uint32_t (&rn)[N], float2 (&pn)[N / 2], const float2 (&pc)[N / 2],
+                                                   const float2 c2, const float2 neg_hi, const float2 neg_128f,
+                                                   float2 (&sum)[4], uint32_t (&packed)[N / 4]) {
+#pragma unroll
+  for (int g = 0; g < N / 4; ++g) {
+    const float2 x01 = make_float2(__uint_as_float(rn[4 * g]), __uint_as_float(rn[4 * g + 1]));
+    const float2 x23 = make_float2(__uint_as_float(rn[4 * g + 2]), __uint_as_float(rn[4 * g + 3]));
+    const float2 a01 = __ffma2_rn(x01, c2, neg_hi);
+    const float2 a23 = __ffma2_rn(x23, c2, neg_hi);
+    const float2 magic2 = make_float2(kMagic, kMagic);
+    float2 n01, n23;
+    n01.x = ex2_approx(a01.x);
+    sum[(2 * g) & 3] = __fadd2_rn(sum[(2 * g) & 3], pc[2 * g]);
+    sum[(2 * g + 1) & 3] = __fadd2_rn(sum[(2 * g + 1) & 3], pc[2 * g + 1]);
+    n01.y = ex2_approx(a01.y);
+    const float2 y01 = __ffma2_rn(pc[2 * g], neg_128f, magic2);
+    const float2 y23 = __ffma2_rn(pc[2 * g + 1], neg_128f, magic2);
+    n23.x = ex2_approx(a23.x);
+    const uint32_t lo = __byte_perm(__float_as_uint(y01.x), __float_as_uint(y01.y), 0x0040);
+    const uint32_t hi = __byte_perm(__float_as_uint(y23.x), __float_as_uint(y23.y), 0x0040);
+    n23.y = ex2_approx(a23.y);
+    packed[g] = __byte_perm(lo, hi, 0x5410);
+    pn[2 * g] = n01;
+    pn[2 * g + 1] = n23;
+  }
+}
 
+// Constants of one row of one tile, derived from the biased integer row maximum.
+struct RowConsts {
+  float2 c2, neg_hi, neg_128f;
+  float f, m_tile;
+};
+__device__ __forceinline__ RowConsts row_consts(const int imax, const float c2s, const float row_scale, const float scale_qk) {
   // exponent argument (s - smax) * c2 = x * c2 - M * c2 with x = kMagic + s and M = kMagic + smax.
   // M * c2 = hi + lo exactly (lo is the rounding residual); the factor 2^-lo is folded into the
   // quantisation constant and the row sum, so nothing is lost and nothing is paid per element.
+  RowConsts k;
   const float M = __uint_as_float(static_cast<uint32_t>(imax));
-  const float hi = M * p.c2;
-  const float lo = fmaf(M, p.c2, -hi);
-  const float f = fmaf(-lo, 0.6931471805599453f, 1.0f);
-  const float2 c2 = make_float2(p.c2, p.c2), neg_hi = make_float2(-hi, -hi), neg_128f = make_float2(-128.f * f, -128.f * f);
-  float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
-  uint32_t packed[8];
-  tmem_ld_fence(ra); tmem_ld32_issue(tS + 32, rb); chunk_exp_pack<false>(ra, 0u, c2, neg_hi, neg_128f, sum_a, sum_b, packed); tmem_st8(tS, packed);
-  tmem_ld_fence(rb); tmem_ld32_issue(tS + 64, ra); chunk_exp_pack<false>(rb, 0u, c2, neg_hi, neg_128f, sum_a, sum_b, packed); tmem_st8(tS + 8, packed);
-  tmem_ld_fence(ra); tmem_ld32_issue(tS + 96, rb); chunk_exp_pack<false>(ra, 0u, c2, neg_hi, neg_128f, sum_a, sum_b, packed); tmem_st8(tS + 16, packed);
-  tmem_ld_fence(rb);                               chunk_exp_pack<false>(rb, 0u, c2, neg_hi, neg_128f, sum_a, sum_b, packed); tmem_st8(tS + 24, packed);
-
-  TileStats st;
+  const float hi = M * c2s;
+  const float lo = fmaf(M, c2s, -hi);
+  k.f = fmaf(-lo, 0.6931471805599453f, 1.0f);
+  k.c2 = make_float2(c2s, c2s);
+  k.neg_hi = make_float2(-hi, -hi);
+  k.neg_128f = make_float2(-128.f * k.f, -128.f * k.f);
   // the value the reference computes for the maximal element (inc/fmha_i8.cuh:196)
-  st.m_tile = (p.row_scale * static_cast<float>(imax - static_cast<int>(kMagicBits))) * p.scale_qk;
-  st.l_tile = f * ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
+  k.m_tile = (row_scale * static_cast<float>(imax - static_cast<int>(kMagicBits))) * scale_qk;
+  return k;
+}
+
+// S row (tensor memory) -> statistics + quantised P row (tensor memory, over the front of S).
+// Fast path: no masked key in the tile.  The eight 16-column chunks are double-buffered so that a
+// tensor-memory load is always in flight while the previous chunk is processed.
+__device__ __forceinline__ TileStats softmax_tile_fast(const uint32_t tS, const FwdParams& p, const int trace_slot = 0, const int trace_idx = 0) {
+  uint32_t ra[16], rb[16];
+  int max_a = INT_MIN, max_b = INT_MIN;
+  {
+    // pass 1 has almost no work per element, so it is bound by the tensor-memory round trip
+    // (about 200 cycles): two wide loads instead of many narrow ones
+    uint32_t wide[64];
+    tmem_ld64_issue(tS, wide);
+    tmem_ld_fence(wide);
+    chunk_max<false, 64>(wide, 0u, max_a, max_b);
+    tmem_ld64_issue(tS + 64, wide);
+    tmem_ld_fence(wide);
+    tmem_ld16_issue(tS, ra);                 // first chunk of pass 2, in flight during the second half of the max
+    chunk_max<false, 64>(wide, 0u, max_a, max_b);
+  }
+  const RowConsts k = row_consts(max(max_a, max_b), p.c2, p.row_scale, p.scale_qk);
+  if ((threadIdx.x >> 5 & 3) == FMHA_TRACE_Q) FMHA_STAMP(trace_slot, trace_idx);
+  float2 sum[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+  uint32_t packed[4];
+  float2 pa[8], pb[8];
+  // pass 2: software pipeline over eight 16-column chunks: the exponentials of chunk c+1 are issued
+  // together with the packing of chunk c, and the load of chunk c+2 is in flight meanwhile
+  tmem_ld_fence(ra); tmem_ld16_issue(tS + 16, rb);
+  chunk_exp<16>(ra, k.c2, k.neg_hi, pa);
+#pragma unroll
+  for (int c = 0; c < 8; c += 2) {
+    tmem_ld_fence(rb); if (c + 2 < 8) tmem_ld16_issue(tS + (c + 2) * 16, ra);
+    chunk_exp_and_pack<16>(rb, pb, pa, k.c2, k.neg_hi, k.neg_128f, sum, packed); tmem_st4(tS + c * 4, packed);
+    if (c + 2 < 8) {
+      tmem_ld_fence(ra); tmem_ld16_issue(tS + (c + 3) * 16, rb);
+      chunk_exp_and_pack<16>(ra, pa, pb, k.c2, k.neg_hi, k.neg_128f, sum, packed); tmem_st4(tS + (c + 1) * 4, packed);
+    } else {
+      chunk_pack<16>(pb, k.neg_128f, sum, packed); tmem_st4(tS + (c + 1) * 4, packed);
+    }
+  }
+  TileStats st;
+  st.m_tile = k.m_tile;
+  st.l_tile = k.f * (((sum[0].x + sum[0].y) + (sum[1].x + sum[1].y)) + ((sum[2].x + sum[2].y) + (sum[3].x + sum[3].y)));
   return st;
 }
 
 // Per-key path for tiles that contain masked keys: compact (rolled) code, used at most once per row
 // with valid-length padding.
 __device__ __forceinline__ TileStats softmax_tile_mixed(const uint32_t tS, const float c2s, const float row_scale,
-                                                     const float scale_qk, const uint32_t* mask_words) {
+                                                        const float scale_qk, const uint32_t* mask_words) {
   uint32_t r[32];
-  int imax = INT_MIN;
+  int max_a = INT_MIN, max_b = INT_MIN;
 #pragma unroll 1
   for (int c = 0; c < 4; ++c) {
     tmem_ld32(tS + c * 32, r);
-    imax = chunk_max<true>(r, mask_words[c], imax);
+    chunk_max<true, 32>(r, mask_words[c], max_a, max_b);
   }
-  const float M = __uint_as_float(static_cast<uint32_t>(imax));
-  const float hi = M * c2s;
-  const float lo = fmaf(M, c2s, -hi);
-  const float f = fmaf(-lo, 0.6931471805599453f, 1.0f);
-  const float2 c2 = make_float2(c2s, c2s), neg_hi = make_float2(-hi, -hi), neg_128f = make_float2(-128.f * f, -128.f * f);
-  float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+  const RowConsts k = row_consts(max(max_a, max_b), c2s, row_scale, scale_qk);
+  float2 sum[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll 1
   for (int c = 0; c < 4; ++c) {
     uint32_t packed[8];
     tmem_ld32(tS + c * 32, r);
-    chunk_exp_pack<true>(r, mask_words[c], c2, neg_hi, neg_128f, sum_a, sum_b, packed);
+    chunk_exp_pack<true, 32>(r, mask_words[c], k.c2, k.neg_hi, k.neg_128f, sum, packed);
     tmem_st8(tS + c * 8, packed);
   }
   TileStats st;
-  st.m_tile = (row_scale * static_cast<float>(imax - static_cast<int>(kMagicBits))) * scale_qk;
-  st.l_tile = f * ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
+  st.m_tile = k.m_tile;
+  st.l_tile = k.f * (((sum[0].x + sum[0].y) + (sum[1].x + sum[1].y)) + ((sum[2].x + sum[2].y) + (sum[3].x + sum[3].y)));
   return st;
 }
 
-// o2 (+)= e_cur * (P8 . V) for 32 output columns; x = raw accumulator read as float = kMagic + O~neg.
-__device__ __forceinline__ void drain_chunk(const uint32_t (&r)[32], float2* o2, const float2 neg_ec, const float2 e_bias, const float2 e_old) {
+// o2 (+)= e_cur * (P8 . V) for N output columns; x = raw accumulator read as float = kMagic + O~neg.
+template <int N>
+__device__ __forceinline__ void drain_chunk(const uint32_t (&r)[N], float2* o2, const float2 neg_ec, const float2 e_bias, const float2 e_old) {
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
+  for (int i = 0; i < N / 2; ++i) {
     const float2 x = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
     const float2 t = __ffma2_rn(x, neg_ec, e_bias);          // e_cur * (P8 . V), exact product before rounding
     o2[i] = __ffma2_rn(o2[i], e_old, t);
@@ -299,13 +398,15 @@ __device__ __forceinline__ void softmax_rows(const FwdParams& p, FwdCtl<FwdCfg<D
     ok = __all_sync(0xFFFFFFFFu, mbar_wait(bar_s, ph, abort_flag));
     if (!ok) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_S_READY, j); break; }
     tc_fence_after();
+    if ((threadIdx.x >> 5 & 3) == FMHA_TRACE_Q) FMHA_STAMP(w * 4 + 0, j);
 
     TileStats st;
     if (ctl->mixed[j] != 0) st = softmax_tile_mixed(tS, p.c2, p.row_scale, p.scale_qk, &ctl->maskbits[4 * ctl->live[j]]);
-    else st = softmax_tile_fast(tS, p);
+    else st = softmax_tile_fast(tS, p, 12 + w, j);
     tmem_wait_st();
     tc_fence_before();
     mbar_arrive(bar_p);
+    if ((threadIdx.x >> 5 & 3) == FMHA_TRACE_Q) FMHA_STAMP(w * 4 + 1, j);
 
     // ---- merge of tile statistics (inc/fmha_i8.cuh:301-304)
     const float m_new = fmaxf(m_run, st.m_tile);
@@ -320,21 +421,19 @@ __device__ __forceinline__ void softmax_rows(const FwdParams& p, FwdCtl<FwdCfg<D
     ok = __all_sync(0xFFFFFFFFu, mbar_wait(bar_o, ph, abort_flag));
     if (!ok) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_O_READY, j); break; }
     tc_fence_after();
+    if ((threadIdx.x >> 5 & 3) == FMHA_TRACE_Q) FMHA_STAMP(w * 4 + 2, j);
     {
-      uint32_t ra[32], rb[32];
-      tmem_ld32_issue(tO, ra);
-      if (D == 128) {
-        tmem_ld_fence(ra); tmem_ld32_issue(tO + 32, rb); drain_chunk(ra, o2, neg_ec, e_bias, e_old2);
-        tmem_ld_fence(rb); tmem_ld32_issue(tO + 64, ra); drain_chunk(rb, o2 + 16, neg_ec, e_bias, e_old2);
-        tmem_ld_fence(ra); tmem_ld32_issue(tO + 96, rb); drain_chunk(ra, o2 + 32, neg_ec, e_bias, e_old2);
-        tmem_ld_fence(rb);                               drain_chunk(rb, o2 + 48, neg_ec, e_bias, e_old2);
-      } else {
-        tmem_ld_fence(ra); tmem_ld32_issue(tO + 32, rb); drain_chunk(ra, o2, neg_ec, e_bias, e_old2);
-        tmem_ld_fence(rb);                               drain_chunk(rb, o2 + 16, neg_ec, e_bias, e_old2);
+      uint32_t wide[64];
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tmem_ld64_issue(tO + c * 64, wide);
+        tmem_ld_fence(wide);
+        drain_chunk<64>(wide, o2 + c * 32, neg_ec, e_bias, e_old2);
       }
     }
     tc_fence_before();
     mbar_arrive(bar_f);
+    if ((threadIdx.x >> 5 & 3) == FMHA_TRACE_Q) FMHA_STAMP(w * 4 + 3, j);
   }
 
   // ---- epilogue (inc/fmha_i8.cuh:318-332): normalise, requantise, 16-byte stores
@@ -509,6 +608,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               if (!mbar_wait(smem_u32(&ctl->p_ready[w]), ph, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_P_READY, j); ok = false; break; }
               if (j > 0 && !mbar_wait(smem_u32(&ctl->o_free[w]), ph ^ 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_O_FREE, j); ok = false; break; }
               tc_fence_after();
+              FMHA_STAMP(8 + w * 2, j);
               issue_o(w, s);
               if (w == nq - 1) mma_commit(smem_u32(&ctl->v_empty[s]));
               if (jn < n_live) {
@@ -517,6 +617,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                 }
                 tc_fence_after();
                 // S_w / P_w columns are free again: the tensor pipe runs this thread's MMAs in order
+                FMHA_STAMP(9 + w * 2, j);
                 issue_s(w, sn);
                 if (w == nq - 1) mma_commit(smem_u32(&ctl->k_empty[sn]));
               }
