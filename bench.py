@@ -176,7 +176,7 @@ def run_reference_arm(args, workload):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", default="C3")
     ap.add_argument("--batch", type=int, default=0, help="override the batch size of the workload (profiling)")
@@ -240,16 +240,30 @@ def main():
     if st != pkg.OK:
         raise RuntimeError(f"device status after warm-up: {words}")
 
+    # The timed region is a few milliseconds, shorter than one nvidia-smi poll, so the clock sampler
+    # brackets it with the same steps, untimed, for a quarter of a second on each side.
+    clocks = ClockSampler(physical_gpu_index(local_rank))
+    clocks.__enter__()
+
+    def soak(seconds):
+        t_end = time.perf_counter() + seconds
+        while time.perf_counter() < t_end:
+            for _ in range(8):
+                step()
+            torch.cuda.synchronize()
+
+    soak(0.25)
     launches0 = pkg.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
-        barrier()
-        ev0.record(stream)
-        for _ in range(args.steps):
-            step()
-        ev1.record(stream)
-        barrier()
+    barrier()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step()
+    ev1.record(stream)
+    barrier()
     launches = pkg.launch_count() - launches0
+    soak(0.25)
+    clocks.__exit__(None, None, None)
     ms_total = ev0.elapsed_time(ev1)
     t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
     if world > 1:
@@ -265,8 +279,16 @@ def main():
     int8_peak = 2.0 * peaks["bf16_tflops"]
     local_ms_launch = ms_total / max(launches, 1)
     achieved = w.ops / (local_ms_launch * 1e-3) / 1e12
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "fmha_fwd_d128_c3_b4_traffic.json")
+    if w.D == 128 and w.S == 2048 and w.H == 32 and os.path.exists(tpath):
+        with open(tpath) as f:
+            tj = json.load(f)
+        # measured on a smaller batch of the same shape; DRAM traffic of this kernel is proportional to the batch
+        traffic = (tj["dram_bytes_read_per_launch"] + tj["dram_bytes_write_per_launch"]) * w.B / tj["captured_batch"]
     roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s", "frac": achieved / int8_peak,
-                "traffic": None, "kernel": f"fmha_fwd_kernel<{w.D}>",
+                "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write, scaled from the B=4 capture)",
+                "algorithmic_bytes": w.bytes, "kernel": f"fmha_fwd_kernel<{w.D}>",
                 "peak_source": f"2 x {peaks['source']} dense bf16 ({peaks['bf16_tflops']} TFLOP/s): kind::i8 issues at twice the bf16 rate",
                 "hbm_gbs_achieved": w.bytes / (local_ms_launch * 1e-3) / 1e9, "hbm_gbs_peak": peaks["hbm_gbs"]}
 
