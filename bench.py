@@ -173,6 +173,39 @@ def run_reference_arm(args, workload):
     print(json.dumps(line), flush=True)
 
 
+def run_quantize_bench(args, pkg, w, dev, rank, world):
+    """HBM-bound producer in front of the attention call: fp32 [B,H,S,D] -> amax + int8.
+    Algorithmic bytes per element: 4 (abs-max pass) + 4 + 1 (quantise pass) = 9."""
+    import torch
+    n = w.B * w.H * w.S * w.D
+    g = torch.Generator(device=dev)
+    g.manual_seed(args.seed)
+    x = torch.randn(n, generator=g, device=dev, dtype=torch.float32)
+    out = torch.empty(n, dtype=torch.int8, device=dev)
+    amax = torch.zeros(1, dtype=torch.float32, device=dev)
+    stream = torch.cuda.current_stream()
+    for _ in range(max(args.warmup, 3)):
+        pkg.quantize_f32(stream, x, out, amax)
+    torch.cuda.synchronize()
+    l0 = pkg.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        pkg.quantize_f32(stream, x, out, amax)
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    peaks = read_peaks()
+    gbs = 9.0 * n / (ms * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({"metric": "quantise producer throughput (9 B/element algorithmic)", "value": gbs, "unit": "GB/s", "n_gpus": 1,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32->int8",
+                          "data": "synthetic", "config": {"workload": f"quantize one {w.name} tensor: {n} elements", "l2": "input larger than L2"},
+                          "gpu_launches": pkg.launch_count() - l0,
+                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                                       "traffic": None, "kernel": "quant_absmax_kernel + quant_apply_kernel"}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -185,6 +218,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=0)
+    ap.add_argument("--path", default="attention", choices=["attention", "quantize"],
+                    help="attention = the forward pass (default); quantize = the device-side abs_max + int8 producer")
     args = ap.parse_args()
 
     import __graft_entry__ as ge
@@ -213,6 +248,9 @@ def main():
     args.warmup = max(args.warmup, 3)
 
     pkg.lib()  # fails loudly if the CUDA library is missing
+    if args.path == "quantize":
+        run_quantize_bench(args, pkg, w, dev, rank, world)
+        return
     # ---- inputs: generated and quantised on the device, o_amax calibrated from an fp32 attention
     data = wl.make_int8_torch(w, args.seed + 101 * rank, dev, want_fp32=True)
     _, o_amax = wl.fp32_attention_torch(data["q"], data["k"], data["v"], data["mask"])

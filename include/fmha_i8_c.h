@@ -95,6 +95,15 @@ int fmha_i8_sm100_debug_pv(void* stream, const int desc[4], const void* p, const
 int fmha_i8_sm100_debug_simt(void* stream, const float amax[5], const int desc[4],
                              const void* q, const void* k, const void* v, const void* mask, void* o);
 
+/* Per-tensor symmetric quantisation on the device, the producer step in front of the attention call:
+ * amax = max|x| (abs_max, inc/utils.hpp:31-39) and q[i] = clamp(floor(x[i]*127/amax + 0.5), -127, 127)
+ * (float_quant2_int8, inc/utils.hpp:23-29; the reference does both on the host, test_fmha_i8.cpp:95-110).
+ * x: n floats (device, 16-byte aligned), out: n int8 (device, 16-byte aligned), amax_out: one float on
+ * the device (may be NULL).  Two kernels on `stream`, no synchronisation.  Uses a scratch buffer of
+ * partial maxima that the library allocates per device and keeps (calls on different streams of one
+ * device that overlap in time would share it: serialise them). */
+int fmha_i8_sm100_quantize_f32(void* stream, const float* x, long long n, int8_t* out, float* amax_out);
+
 /* Synchronises the current device, copies out and clears the eight device status words.
  * words[0] == 0 means no kernel of this library gave up on a bounded wait since the last call.
  * Otherwise words[0] = which wait gave up (FMHA_I8_DEV_*), words[1] = block index, words[2] = warp,

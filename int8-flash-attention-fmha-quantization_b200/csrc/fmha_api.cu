@@ -12,6 +12,7 @@
 #include "../../include/fmha_i8_c.h"
 #include "fmha_debug_sm100.cuh"
 #include "fmha_fwd_sm100.cuh"
+#include "fmha_quant_sm100.cuh"
 
 namespace {
 
@@ -203,6 +204,28 @@ struct HostStaging {
 HostStaging g_staging[kMaxDevices];
 std::mutex g_staging_mutex;
 
+// Scratch of fmha_i8_sm100_quantize_f32 (partial maxima), one buffer per device, grown on demand.
+struct QuantScratch {
+  float* partial = nullptr;
+  long long capacity_chunks = 0;
+};
+QuantScratch g_quant_scratch[kMaxDevices];
+std::mutex g_quant_mutex;
+
+int check_quant_args(const float* x, long long n, const int8_t* out) {
+  if (!x || !out) return FMHA_I8_ERR_NULL_POINTER;
+  if (n < 1) return FMHA_I8_ERR_BAD_SHAPE;
+  if (!aligned(x, 16) || !aligned(out, 16)) return FMHA_I8_ERR_MISALIGNED;
+  return FMHA_I8_OK;
+}
+
+int launch_quantize(cudaStream_t stream, const float* x, long long n, int8_t* out, float* amax_out, float* partial, long long n_chunks) {
+  quant_absmax_kernel<<<static_cast<unsigned>(n_chunks), kQuantThreads, 0, stream>>>(x, n, partial);
+  quant_apply_kernel<<<static_cast<unsigned>(n_chunks), kQuantThreads, 0, stream>>>(x, n, partial, static_cast<int>(n_chunks), out, amax_out);
+  g_launch_count.fetch_add(2, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH;
+}
+
 }  // namespace
 
 extern "C" {
@@ -338,6 +361,31 @@ int fmha_i8_sm100_debug_simt(void* stream, const float amax[5], const int desc[4
   else simt_check_kernel<64><<<grid, 128, 0, s>>>(q8, k8, v8, m8, o8, S, H, 0, p.row_scale, p.scale_qk, p.scale_v_out);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
   return finish(cudaGetLastError() == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH);
+}
+
+int fmha_i8_sm100_quantize_f32(void* stream, const float* x, long long n, int8_t* out, float* amax_out) {
+  int st = check_quant_args(x, n, out);
+  if (st != FMHA_I8_OK) return finish(st);
+  int err = FMHA_I8_OK;
+  if (!current_device(&err)) return finish(err);
+  int dev_id = 0;
+  cudaGetDevice(&dev_id);
+  const long long n_chunks = (n + kQuantChunk - 1) / kQuantChunk;
+  if (n_chunks > 0x7FFFFFFFLL) return finish(FMHA_I8_ERR_TOO_LARGE);
+  float* partial = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_quant_mutex);
+    QuantScratch& q = g_quant_scratch[dev_id];
+    if (q.capacity_chunks < n_chunks) {
+      // growing frees the old buffer: wait for work that may still read it
+      if (q.partial) { cudaDeviceSynchronize(); cudaFree(q.partial); q.partial = nullptr; q.capacity_chunks = 0; }
+      const long long cap = n_chunks < 4096 ? 4096 : n_chunks;
+      if (cudaMalloc(&q.partial, sizeof(float) * cap) != cudaSuccess) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
+      q.capacity_chunks = cap;
+    }
+    partial = q.partial;
+  }
+  return finish(launch_quantize(static_cast<cudaStream_t>(stream), x, n, out, amax_out, partial, n_chunks));
 }
 
 int fmha_i8_sm100_device_status(unsigned words[8]) {
