@@ -104,6 +104,23 @@ int fmha_i8_sm100_debug_simt(void* stream, const float amax[5], const int desc[4
  * device that overlap in time would share it: serialise them). */
 int fmha_i8_sm100_quantize_f32(void* stream, const float* x, long long n, int8_t* out, float* amax_out);
 
+/* The same quantisation for callers that must not allocate device memory.  (No counterpart in the
+ * reference project.)  Some hosts of this library hand every byte of the GPU to their own memory pool
+ * when they start, so a cudaMalloc made later by a library either fails or escapes the pool's
+ * accounting; others run a latency-critical loop and cannot afford the device-wide synchronisation that
+ * cudaMalloc and cudaFree imply.  For them the partial maxima are kept in a 16 KB array that is part of
+ * the library's device image: this entry point calls no cudaMalloc, no cudaFree and nothing else that
+ * allocates.
+ *   - Limit: n <= 268,435,456 elements (4096 chunks of 65536); larger tensors are refused with
+ *     FMHA_I8_ERR_TOO_LARGE and one line on stderr.
+ *   - The first call on each device looks up the device address of that array (with that device
+ *     current); make that first call before any stream capture begins.
+ *   - All calls on one device share the one array.  Nothing in it has to be cleared between calls (each
+ *     call overwrites every slot it later reads), but two calls whose kernels overlap on the GPU --
+ *     different streams without an ordering between them -- race on it: keep them ordered.
+ * Arguments and results are those of fmha_i8_sm100_quantize_f32. */
+int fmha_i8_sm100_quantize_f32_noalloc(void* stream, const float* x, long long n, int8_t* out, float* amax_out);
+
 /* Synchronises the current device, copies out and clears the eight device status words.
  * words[0] == 0 means no kernel of this library gave up on a bounded wait since the last call.
  * Otherwise words[0] = which wait gave up (FMHA_I8_DEV_*), words[1] = block index, words[2] = warp,

@@ -31,7 +31,7 @@ FLAG_USE_TCU = 1
 EXPORTS = (
     "fmha_i8_sm100_infer", "fmha_i8_sm100_infer_slice", "fmha_i8_sm100_infer_host",
     "fmha_i8_sm100_debug_qk", "fmha_i8_sm100_debug_pv", "fmha_i8_sm100_debug_simt",
-    "fmha_i8_sm100_quantize_f32", "fmha_i8_sm100_device_status", "fmha_i8_sm100_last_status", "fmha_i8_sm100_status_string",
+    "fmha_i8_sm100_quantize_f32", "fmha_i8_sm100_quantize_f32_noalloc", "fmha_i8_sm100_device_status", "fmha_i8_sm100_last_status", "fmha_i8_sm100_status_string",
     "fmha_i8_sm100_launch_count", "fmha_i8_sm100_version",
 )
 
@@ -86,6 +86,7 @@ def lib():
         L.fmha_i8_sm100_debug_pv.argtypes = [vp, ip, vp, vp, vp, u]
         L.fmha_i8_sm100_debug_simt.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp]
         L.fmha_i8_sm100_quantize_f32.argtypes = [vp, vp, ctypes.c_longlong, vp, vp]
+        L.fmha_i8_sm100_quantize_f32_noalloc.argtypes = [vp, vp, ctypes.c_longlong, vp, vp]
         L.fmha_i8_sm100_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         L.fmha_i8_sm100_status_string.restype = ctypes.c_char_p
         L.fmha_i8_sm100_status_string.argtypes = [ctypes.c_int]
@@ -175,7 +176,9 @@ def debug_simt(stream, fmha_param, attn_desc, q, k, v, padding_mask, o):
 
 def quantize_f32(stream, x, out, amax_out=None, n=None, entry="fmha_i8_sm100_quantize_f32"):
     """Device-side abs_max + float_quant2_int8 (reference inc/utils.hpp:23-39): x float32 -> out int8,
-    amax written to the one-element device tensor `amax_out`.  Enqueues on `stream`, no synchronisation."""
+    amax written to the one-element device tensor `amax_out`.  Enqueues on `stream`, no synchronisation.
+    entry="fmha_i8_sm100_quantize_f32_noalloc" selects the variant that never allocates device memory
+    (built-in scratch, at most 268,435,456 elements, calls on one device must not overlap)."""
     count = int(n if n is not None else x.numel())
     st = getattr(lib(), entry)(_stream_handle(stream), _ptr(x), count, _ptr(out), _ptr(amax_out))
     if st != OK:

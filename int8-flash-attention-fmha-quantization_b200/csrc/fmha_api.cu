@@ -219,6 +219,15 @@ int check_quant_args(const float* x, long long n, const int8_t* out) {
   return FMHA_I8_OK;
 }
 
+// Scratch of fmha_i8_sm100_quantize_f32_noalloc: the partial maxima live in the library's own device
+// image instead of the heap.  Every GPU that loads the library carries these 16 KB until the process
+// exits.  4096 chunks x 65536 elements = 268,435,456 elements (1 GiB of fp32) is the largest tensor
+// the entry point accepts.
+constexpr long long kNoAllocMaxChunks = 4096;
+static __device__ __align__(256) float g_quant_partial_static[kNoAllocMaxChunks];
+float* g_quant_static_ptr[kMaxDevices];      // device address of the array above, per device (0 = not looked up yet)
+std::mutex g_quant_static_mutex;
+
 int launch_quantize(cudaStream_t stream, const float* x, long long n, int8_t* out, float* amax_out, float* partial, long long n_chunks) {
   quant_absmax_kernel<<<static_cast<unsigned>(n_chunks), kQuantThreads, 0, stream>>>(x, n, partial);
   quant_apply_kernel<<<static_cast<unsigned>(n_chunks), kQuantThreads, 0, stream>>>(x, n, partial, static_cast<int>(n_chunks), out, amax_out);
@@ -385,6 +394,39 @@ int fmha_i8_sm100_quantize_f32(void* stream, const float* x, long long n, int8_t
     }
     partial = q.partial;
   }
+  return finish(launch_quantize(static_cast<cudaStream_t>(stream), x, n, out, amax_out, partial, n_chunks));
+}
+
+int fmha_i8_sm100_quantize_f32_noalloc(void* stream, const float* x, long long n, int8_t* out, float* amax_out) {
+  int st = check_quant_args(x, n, out);
+  if (st != FMHA_I8_OK) return finish(st);
+  const long long n_chunks = (n + kQuantChunk - 1) / kQuantChunk;
+  if (n_chunks > kNoAllocMaxChunks) {
+    std::fprintf(stderr, "fmha_i8_sm100_quantize_f32_noalloc: %lld elements exceed the built-in scratch (at most %lld)\n", n,
+                 kNoAllocMaxChunks * kQuantChunk);
+    return finish(FMHA_I8_ERR_TOO_LARGE);
+  }
+  int err = FMHA_I8_OK;
+  if (!current_device(&err)) return finish(err);
+  int dev_id = 0;
+  if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= kMaxDevices) return finish(FMHA_I8_ERR_LAUNCH);
+  float* partial = nullptr;
+  {
+    // One-time set-up per device, done by the first call on that device with the device current:
+    // in host code the array's name is only a handle, the kernels need its device address.
+    std::lock_guard<std::mutex> lock(g_quant_static_mutex);
+    if (!g_quant_static_ptr[dev_id]) {
+      float* ptr = nullptr;
+      if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_quant_partial_static) != cudaSuccess || !ptr) {
+        cudaGetLastError();
+        return finish(FMHA_I8_ERR_LAUNCH);
+      }
+      g_quant_static_ptr[dev_id] = ptr;
+    }
+    partial = g_quant_static_ptr[dev_id];
+  }
+  // Nothing in the scratch has to start at zero: pass 1 overwrites every slot that pass 2 reads
+  // (slots [0, n_chunks)); what an earlier, larger call left beyond them is never looked at.
   return finish(launch_quantize(static_cast<cudaStream_t>(stream), x, n, out, amax_out, partial, n_chunks));
 }
 
