@@ -72,8 +72,9 @@ int fmha_i8_sm100_infer_slice(void* stream, const float amax[5], const int desc[
 
 /* End-to-end form of the caller in test_fmha_i8.cpp:165-178,204,236: HOST buffers in, HOST
  * buffer out.  Copies q,k,v,mask to device staging buffers owned by the library (grown on demand,
- * kept for reuse), runs the forward pass, copies o back and synchronises.  Pinned host memory
- * makes the copies asynchronous to each other; pageable memory works too. */
+ * kept for reuse), runs the forward pass, copies o back and synchronises.  The work is pipelined
+ * over up to eight ranges of heads on three internal streams, so with pinned host memory the
+ * inbound copies, the kernels and the outbound copies overlap; pageable memory works too. */
 int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4],
                              const void* host_q, const void* host_k, const void* host_v,
                              const void* host_mask, void* host_o, unsigned flags);

@@ -84,6 +84,17 @@ int set_kernel_attributes(DeviceInfo* d) {
   set(reinterpret_cast<const void*>(&debug_pv_kernel<128, true>), pv_smem_bytes<128>());
   set(reinterpret_cast<const void*>(&debug_pv_kernel<128, false>), pv_smem_bytes<128>());
   if (e != cudaSuccess) { cudaGetLastError(); return FMHA_I8_ERR_LAUNCH; }
+  // The forward kernel redistributes registers with setmaxnreg; that only terminates if the launch
+  // allocation is the one the targets were sized for.
+  cudaFuncAttributes fa64{}, fa128{};
+  if (cudaFuncGetAttributes(&fa64, reinterpret_cast<const void*>(&fmha_fwd_kernel<64>)) != cudaSuccess ||
+      cudaFuncGetAttributes(&fa128, reinterpret_cast<const void*>(&fmha_fwd_kernel<128>)) != cudaSuccess ||
+      fa64.numRegs != kLaunchRegs || fa128.numRegs != kLaunchRegs) {
+    cudaGetLastError();
+    std::fprintf(stderr, "fmha_i8_sm100: forward kernel built with %d/%d registers per thread, expected %d; refusing to launch\n",
+                 fa64.numRegs, fa128.numRegs, kLaunchRegs);
+    return FMHA_I8_ERR_LAUNCH;
+  }
   d->attr_set = true;
   return FMHA_I8_OK;
 }
@@ -195,11 +206,15 @@ int infer_slice_impl(void* stream, const float amax[5], const int desc[4], const
   return desc[3] == 128 ? launch_fwd<128>(s, dev, p, q, k, v) : launch_fwd<64>(s, dev, p, q, k, v);
 }
 
-// Device staging buffers of fmha_i8_sm100_infer_host, one set per device, grown on demand.
+// Device staging buffers of fmha_i8_sm100_infer_host, one set per device, grown on demand, plus the
+// three streams and the events of its copy/compute pipeline.
+constexpr int kHostChunks = 8;
 struct HostStaging {
   void* q = nullptr; void* k = nullptr; void* v = nullptr; void* o = nullptr; void* mask = nullptr;
   size_t tensor_cap = 0, mask_cap = 0;
-  cudaStream_t stream = nullptr;
+  cudaStream_t s_in = nullptr, s_run = nullptr, s_out = nullptr;
+  cudaEvent_t landed[kHostChunks] = {}, computed[kHostChunks] = {};
+  bool ready = false;
 };
 HostStaging g_staging[kMaxDevices];
 std::mutex g_staging_mutex;
@@ -263,7 +278,16 @@ int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void*
   const size_t mask_bytes = static_cast<size_t>(desc[0]) * desc[1];
   std::lock_guard<std::mutex> lock(g_staging_mutex);
   HostStaging& s = g_staging[dev_id];
-  if (!s.stream && cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess) return finish(FMHA_I8_ERR_LAUNCH);
+  if (!s.ready) {
+    bool good = cudaStreamCreateWithFlags(&s.s_in, cudaStreamNonBlocking) == cudaSuccess &&
+                cudaStreamCreateWithFlags(&s.s_run, cudaStreamNonBlocking) == cudaSuccess &&
+                cudaStreamCreateWithFlags(&s.s_out, cudaStreamNonBlocking) == cudaSuccess;
+    for (int i = 0; i < kHostChunks && good; ++i)
+      good = cudaEventCreateWithFlags(&s.landed[i], cudaEventDisableTiming) == cudaSuccess &&
+             cudaEventCreateWithFlags(&s.computed[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!good) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
+    s.ready = true;
+  }
   if (s.tensor_cap < tensor_bytes) {
     cudaFree(s.q); cudaFree(s.k); cudaFree(s.v); cudaFree(s.o);
     s.q = s.k = s.v = s.o = nullptr;
@@ -282,16 +306,39 @@ int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void*
     if (cudaMalloc(&s.mask, mask_bytes) != cudaSuccess) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
     s.mask_cap = mask_bytes;
   }
-  cudaError_t e = cudaMemcpyAsync(s.q, host_q, tensor_bytes, cudaMemcpyHostToDevice, s.stream);
-  if (e == cudaSuccess) e = cudaMemcpyAsync(s.k, host_k, tensor_bytes, cudaMemcpyHostToDevice, s.stream);
-  if (e == cudaSuccess) e = cudaMemcpyAsync(s.mask, host_mask, mask_bytes, cudaMemcpyHostToDevice, s.stream);
-  if (e == cudaSuccess) e = cudaMemcpyAsync(s.v, host_v, tensor_bytes, cudaMemcpyHostToDevice, s.stream);
-  if (e != cudaSuccess) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
-  st = infer_slice_impl(s.stream, amax, desc, s.q, s.k, s.v, s.mask, s.o, 0, desc[0] * desc[2], flags);
+  // Pipeline over contiguous ranges of heads: while chunk i is computed, chunk i+1 is on its way in and
+  // chunk i-1 on its way out (the bus is full duplex).  Each chunk is one fmha_i8_sm100_infer_slice.
+  const int BH = desc[0] * desc[2];
+  const int n_chunks = BH < kHostChunks ? BH : kHostChunks;
+  const size_t head_bytes = static_cast<size_t>(desc[1]) * desc[3];
+  cudaError_t e = cudaMemcpyAsync(s.mask, host_mask, mask_bytes, cudaMemcpyHostToDevice, s.s_in);
+  for (int i = 0; i < n_chunks && e == cudaSuccess; ++i) {
+    const int begin = static_cast<int>(static_cast<long long>(BH) * i / n_chunks);
+    const int end = static_cast<int>(static_cast<long long>(BH) * (i + 1) / n_chunks);
+    const size_t off = begin * head_bytes, bytes = (end - begin) * head_bytes;
+    const char* hq = static_cast<const char*>(host_q) + off;
+    const char* hk = static_cast<const char*>(host_k) + off;
+    const char* hv = static_cast<const char*>(host_v) + off;
+    char* dq = static_cast<char*>(s.q) + off;
+    char* dk = static_cast<char*>(s.k) + off;
+    char* dv = static_cast<char*>(s.v) + off;
+    char* dout = static_cast<char*>(s.o) + off;
+    e = cudaMemcpyAsync(dq, hq, bytes, cudaMemcpyHostToDevice, s.s_in);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dk, hk, bytes, cudaMemcpyHostToDevice, s.s_in);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dv, hv, bytes, cudaMemcpyHostToDevice, s.s_in);
+    if (e == cudaSuccess) e = cudaEventRecord(s.landed[i], s.s_in);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(s.s_run, s.landed[i], 0);
+    if (e != cudaSuccess) break;
+    st = infer_slice_impl(s.s_run, amax, desc, dq, dk, dv, s.mask, dout, begin, end - begin, flags);
+    if (st != FMHA_I8_OK) break;
+    e = cudaEventRecord(s.computed[i], s.s_run);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(s.s_out, s.computed[i], 0);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(static_cast<char*>(host_o) + off, dout, bytes, cudaMemcpyDeviceToHost, s.s_out);
+  }
+  // drain all three streams whatever happened, so the staging buffers are idle when the lock is released
+  const cudaError_t e1 = cudaStreamSynchronize(s.s_in), e2 = cudaStreamSynchronize(s.s_run), e3 = cudaStreamSynchronize(s.s_out);
   if (st != FMHA_I8_OK) return finish(st);
-  e = cudaMemcpyAsync(host_o, s.o, tensor_bytes, cudaMemcpyDeviceToHost, s.stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(s.stream);
-  if (e != cudaSuccess) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
+  if (e != cudaSuccess || e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
   return finish(FMHA_I8_OK);
 }
 

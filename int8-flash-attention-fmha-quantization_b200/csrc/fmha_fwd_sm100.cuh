@@ -58,8 +58,15 @@ constexpr int kMaxTiles = kMaxSeq / kTile;
 constexpr int kFwdThreads = 384;     // three warpgroups
 constexpr int kWarpLoad = 8;
 constexpr int kWarpMma = 9;
-constexpr int kRegsSoftmax = 224;    // 8 warps x 224 + 4 warps x 56 = 2016 <= 2048 warp-registers
+// setmaxnreg moves registers inside the CTA's own launch allocation (registers per thread at launch x
+// threads), not inside the SM's whole register file: a request that does not fit blocks forever.  With
+// 384 threads the compiler's launch allocation is 168 registers per thread (the host checks this before
+// the first launch and refuses otherwise): 8 warps x 224 + 4 warps x 56 = 12 x 168.
+constexpr int kLaunchRegs = 168;
+constexpr int kRegsSoftmax = 224;
 constexpr int kRegsOther = 56;
+static_assert(8 * kRegsSoftmax + 4 * kRegsOther <= (kFwdThreads / 32) * kLaunchRegs,
+              "setmaxnreg targets exceed the CTA's register allocation: the kernel would hang");
 constexpr uint32_t kTmemCols = 512;
 constexpr float kMagic = 12582912.0f;          // 1.5 * 2^23: float whose ulp is 1 over [2^23, 2^24)
 constexpr uint32_t kMagicBits = 0x4B400000u;
