@@ -50,7 +50,8 @@ enum {
   FMHA_I8_DEV_WAIT_P_READY = 7,    /* MMA issuer waiting for the quantised P */
   FMHA_I8_DEV_WAIT_O_READY = 8,    /* softmax waiting for P.V */
   FMHA_I8_DEV_WAIT_O_FREE = 9,     /* MMA issuer waiting for the previous P.V to be drained */
-  FMHA_I8_DEV_WAIT_DEBUG = 10      /* a wait inside a debug kernel */
+  FMHA_I8_DEV_WAIT_DEBUG = 10,     /* a wait inside a debug kernel */
+  FMHA_I8_DEV_WAIT_INFO = 11       /* a role waiting for (or the scanner waiting to reuse) a unit's mask information */
 };
 
 #define FMHA_I8_FLAG_USE_TCU 1u    /* mirrors the reference's use_tcu argument; must be set */

@@ -33,6 +33,7 @@ constexpr int kMaxDevices = 64;
 struct DeviceInfo {
   int checked = 0;      // 0 = not yet, 1 = sm_100, -1 = something else
   unsigned* status = nullptr;
+  int sm_count = 0;
   bool attr_set = false;
 };
 DeviceInfo g_dev[kMaxDevices];
@@ -53,6 +54,7 @@ DeviceInfo* current_device(int* err) {
       return nullptr;
     }
     d.checked = (major == 10 && minor == 0) ? 1 : -1;
+    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || d.sm_count < 1) d.sm_count = 1;
   }
   if (d.checked < 0) { *err = FMHA_I8_ERR_WRONG_ARCH; return nullptr; }
   if (!d.status) {
@@ -172,7 +174,8 @@ int launch_fwd(cudaStream_t stream, DeviceInfo* dev, FwdParams p, const void* q,
   if ((st = make_map(&mq, q, p.bh_count, p.S, D)) != FMHA_I8_OK) return st;
   if ((st = make_map(&mk, k, p.bh_count, p.S, D)) != FMHA_I8_OK) return st;
   if ((st = make_map(&mv, v, p.bh_count, p.S, D)) != FMHA_I8_OK) return st;
-  const unsigned grid = static_cast<unsigned>(p.bh_count) * static_cast<unsigned>(p.q_pairs);
+  // persistent CTAs: one per SM (tensor memory is allocated whole), each walking its share of the units
+  const unsigned grid = static_cast<unsigned>(p.n_units < dev->sm_count ? p.n_units : dev->sm_count);
   fmha_fwd_kernel<D><<<grid, kFwdThreads, fwd_smem_bytes<D>(), stream>>>(mq, mk, mv, p);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH;
@@ -201,6 +204,11 @@ int infer_slice_impl(void* stream, const float amax[5], const int desc[4], const
   p.bh_begin = bh_begin;
   p.bh_count = bh_count;
   p.q_pairs = (p.S + 2 * kTile - 1) / (2 * kTile);
+  {
+    const long long units = static_cast<long long>(bh_count) * p.q_pairs;
+    if (units > 0x7FFFFFFFLL) return FMHA_I8_ERR_BAD_SHAPE;
+    p.n_units = static_cast<int>(units);
+  }
   p.status = dev->status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return desc[3] == 128 ? launch_fwd<128>(s, dev, p, q, k, v) : launch_fwd<64>(s, dev, p, q, k, v);

@@ -58,6 +58,7 @@ constexpr int kMaxTiles = kMaxSeq / kTile;
 constexpr int kFwdThreads = 384;     // three warpgroups
 constexpr int kWarpLoad = 8;
 constexpr int kWarpMma = 9;
+constexpr int kWarpScan = 10;         // prepares the next unit's mask information
 // setmaxnreg moves registers inside the CTA's own launch allocation (registers per thread at launch x
 // threads), not inside the SM's whole register file: a request that does not fit blocks forever.  With
 // 384 threads the compiler's launch allocation is 168 registers per thread (the host checks this before
@@ -83,6 +84,7 @@ struct FwdParams {
   const int8_t* mask;   // [B,S] whole mask
   int8_t* o;            // first head of the slice
   int S, H, bh_begin, bh_count, q_pairs;
+  int n_units;          // bh_count * q_pairs work units, taken round-robin by the resident CTAs
   float row_scale;      // 1/sqrt(D), the reference's constant (inc/fmha_i8.cuh:71)
   float scale_qk;       // q_amax*k_amax/127^2 (inc/fmha_i8.cuh:72)
   float scale_v_out;    // v_amax/(o_amax*128) (inc/fmha_i8.cuh:318)
@@ -90,16 +92,24 @@ struct FwdParams {
   unsigned* status;     // eight device status words
 };
 
+// What every role needs to know about one work unit's padding mask.  Two of these live in shared
+// memory: the scanner warp fills the one of the NEXT unit while the current unit is being processed.
+struct UnitInfo {
+  int n_live;                         // key tiles with at least one unmasked key
+  uint32_t maskbits[kMaxTiles * 4];   // bit set = key masked (or beyond seq_len)
+  uint16_t live[kMaxTiles];           // indices of the live key tiles, ascending
+  uint8_t mixed[kMaxTiles];           // 1 = that live tile has masked keys too
+};
+constexpr int kInfoConsumers = 10;    // loader, MMA issuer and the eight softmax warps each release an info buffer once
+
 template <int NS> struct FwdCtl {
-  uint64_t q_full;
+  uint64_t q_full, q_empty;
   uint64_t k_full[NS], k_empty[NS], v_full[NS], v_empty[NS];
   uint64_t s_full[2], p_ready[2], o_full[2], o_free[2];
+  uint64_t info_full[2], info_empty[2];
   uint32_t tmem_base;
   int abort;
-  int n_live;
-  uint32_t maskbits[kMaxTiles * 4];   // bit set = key masked (or beyond seq_len)
-  uint16_t live[kMaxTiles];           // indices of key tiles that have at least one unmasked key
-  uint8_t mixed[kMaxTiles];           // 1 = that live tile has masked keys too
+  UnitInfo info[2];
 };
 
 __device__ __noinline__ void raise_status(volatile int* abort_flag, unsigned* status, unsigned code, unsigned tile) {
@@ -119,12 +129,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-// Builds the per-CTA view of one batch's padding mask: 128-bit masks per key tile, the list of
-// live tiles and whether each needs the per-key path.
-template <class Ctl>
-__device__ void scan_mask(Ctl* ctl, const int8_t* mask_row, int S, int n_tiles) {
+// Builds one unit's view of its batch's padding mask: 128-bit masks per key tile, the list of live
+// tiles and whether each needs the per-key path.  Executed by ONE warp.
+__device__ __forceinline__ void scan_mask_warp(UnitInfo* info, const int8_t* mask_row, int S, int n_tiles) {
+  const int lane = threadIdx.x & 31;
   const uint32_t* words = reinterpret_cast<const uint32_t*>(mask_row);
-  for (int g = threadIdx.x; g < n_tiles * 4; g += blockDim.x) {
+  for (int g = lane; g < n_tiles * 4; g += 32) {
     const int key0 = g * 32;
     uint32_t bits = 0xFFFFFFFFu;
     if (key0 < S) {  // S is a multiple of 64, so a 32-key group is entirely inside or outside
@@ -137,21 +147,28 @@ __device__ void scan_mask(Ctl* ctl, const int8_t* mask_row, int S, int n_tiles) 
           if ((wv >> (8 * b)) & 0xFFu) bits |= 1u << (4 * i + b);
       }
     }
-    ctl->maskbits[g] = bits;
+    info->maskbits[g] = bits;
   }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int n = 0;
-    for (int t = 0; t < n_tiles; ++t) {
-      const uint32_t a = ctl->maskbits[4 * t], b = ctl->maskbits[4 * t + 1], c = ctl->maskbits[4 * t + 2], d = ctl->maskbits[4 * t + 3];
-      if ((a & b & c & d) != 0xFFFFFFFFu) {
-        ctl->live[n] = static_cast<uint16_t>(t);
-        ctl->mixed[n] = ((a | b | c | d) != 0u) ? 1 : 0;
-        ++n;
-      }
+  __syncwarp();
+  int n = 0;
+  for (int base = 0; base < n_tiles; base += 32) {
+    const int t = base + lane;
+    bool is_live = false, is_mixed = false;
+    if (t < n_tiles) {
+      const uint32_t a = info->maskbits[4 * t], b = info->maskbits[4 * t + 1], c = info->maskbits[4 * t + 2], d = info->maskbits[4 * t + 3];
+      is_live = (a & b & c & d) != 0xFFFFFFFFu;
+      is_mixed = (a | b | c | d) != 0u;
     }
-    ctl->n_live = n;
+    const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, is_live);
+    if (is_live) {
+      const int pos = n + __popc(ballot & ((1u << lane) - 1u));
+      info->live[pos] = static_cast<uint16_t>(t);
+      info->mixed[pos] = is_mixed ? 1 : 0;
+    }
+    n += __popc(ballot);
   }
+  if (lane == 0) info->n_live = n;
+  __syncwarp();
 }
 
 // Writes the two constant fp16 operands of the bias MMA: A[m][0] = 4096, B[n][0] = 3072, all other
@@ -380,17 +397,19 @@ __device__ __forceinline__ void drain_chunk(const uint32_t (&r)[N], float2* o2, 
   }
 }
 
-// One softmax thread: query row q_row of query tile w.
+// One softmax thread, one work unit: query row q_row of query tile w.  `tiles_done` counts the key tiles
+// this query-tile slot has processed in earlier units of this CTA: the barriers shared with the MMA issuer
+// keep flipping phase across units.  Returns false if a wait gave up.
 template <int D>
-__device__ __forceinline__ void softmax_rows(const FwdParams& p, FwdCtl<FwdCfg<D>::kStages>* ctl, const int w,
-                                             const uint32_t tmem_base, const int q_row, const int bh_local) {
+__device__ __forceinline__ bool softmax_unit(const FwdParams& p, FwdCtl<FwdCfg<D>::kStages>* ctl, const UnitInfo* info, const int w,
+                                             const uint32_t tmem_base, const int q_row, const int bh_local, const uint32_t tiles_done) {
   const int warp = threadIdx.x >> 5;
   const uint32_t lane_field = static_cast<uint32_t>((warp & 3) * 32) << 16;
   const uint32_t tS = tmem_base + lane_field + static_cast<uint32_t>(w * kTile);
   const uint32_t tO = tmem_base + lane_field + static_cast<uint32_t>(2 * kTile + w * D);
   const uint32_t bar_s = smem_u32(&ctl->s_full[w]), bar_p = smem_u32(&ctl->p_ready[w]);
   const uint32_t bar_o = smem_u32(&ctl->o_full[w]), bar_f = smem_u32(&ctl->o_free[w]);
-  const int n_live = ctl->n_live;
+  const int n_live = info->n_live;
   volatile int* abort_flag = &ctl->abort;
 
   float2 o2[D / 2];
@@ -401,14 +420,14 @@ __device__ __forceinline__ void softmax_rows(const FwdParams& p, FwdCtl<FwdCfg<D
 
 #pragma unroll 1
   for (int j = 0; j < n_live; ++j) {
-    const uint32_t ph = static_cast<uint32_t>(j & 1);
+    const uint32_t ph = (tiles_done + static_cast<uint32_t>(j)) & 1u;
     ok = __all_sync(0xFFFFFFFFu, mbar_wait(bar_s, ph, abort_flag));
     if (!ok) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_S_READY, j); break; }
     tc_fence_after();
     if ((threadIdx.x >> 5 & 3) == FMHA_TRACE_Q) FMHA_STAMP(w * 4 + 0, j);
 
     TileStats st;
-    if (ctl->mixed[j] != 0) st = softmax_tile_mixed(tS, p.c2, p.row_scale, p.scale_qk, &ctl->maskbits[4 * ctl->live[j]]);
+    if (info->mixed[j] != 0) st = softmax_tile_mixed(tS, p.c2, p.row_scale, p.scale_qk, &info->maskbits[4 * info->live[j]]);
     else st = softmax_tile_fast(tS, p, 12 + w, j);
     tmem_wait_st();
     tc_fence_before();
@@ -424,7 +443,7 @@ __device__ __forceinline__ void softmax_rows(const FwdParams& p, FwdCtl<FwdCfg<D
     const float2 neg_ec = make_float2(-e_cur, -e_cur), e_bias = make_float2(e_cur * kMagic, e_cur * kMagic);
     const float2 e_old2 = make_float2(e_old, e_old);
 
-    // ---- drain O~ = bias - (P8 . V) into the fp32 running row, double-buffered
+    // ---- drain O~ = bias - (P8 . V) into the fp32 running row
     ok = __all_sync(0xFFFFFFFFu, mbar_wait(bar_o, ph, abort_flag));
     if (!ok) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_O_READY, j); break; }
     tc_fence_after();
@@ -466,8 +485,27 @@ __device__ __forceinline__ void softmax_rows(const FwdParams& p, FwdCtl<FwdCfg<D
       *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
     }
   }
+  return ok;
 }
 
+// Geometry of work unit u.
+struct UnitGeom {
+  int bh_local, batch, q_row0, nq;
+};
+__device__ __forceinline__ UnitGeom unit_geom(const FwdParams& p, int u) {
+  UnitGeom g;
+  g.bh_local = u / p.q_pairs;
+  const int pair = u - g.bh_local * p.q_pairs;
+  g.batch = (p.bh_begin + g.bh_local) / p.H;
+  g.q_row0 = pair * 2 * kTile;
+  g.nq = (g.q_row0 + kTile < p.S) ? 2 : 1;
+  return g;
+}
+
+// Persistent kernel: gridDim.x = min(units, SMs) CTAs; CTA b processes units b, b + gridDim.x, ...
+// Tensor memory, barriers and the bias operands are set up once; the scanner warp prepares the next
+// unit's mask information and the loader prefetches its tiles while the current unit is finishing, so a
+// unit boundary costs about one MMA round trip instead of a CTA launch, a cold TMA load and a pipeline fill.
 template <int D>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -486,13 +524,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t v_smem = k_smem + NS * Cfg::kTileBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int unit = blockIdx.x;
-  const int bh_local = unit / p.q_pairs;
-  const int pair = unit - bh_local * p.q_pairs;
-  const int batch = (p.bh_begin + bh_local) / p.H;
-  const int q_row0 = pair * 2 * kTile;
-  const int nq = (q_row0 + kTile < p.S) ? 2 : 1;
   const int n_tiles = (p.S + kTile - 1) / kTile;
+  const int first_unit = blockIdx.x, unit_step = gridDim.x;
 
   // an earlier CTA already gave up: do not start (decided by one thread so the CTA stays uniform)
   __shared__ int s_go;
@@ -503,6 +536,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (threadIdx.x == 0) {
     ctl->abort = 0;
     mbar_init(smem_u32(&ctl->q_full), 1);
+    mbar_init(smem_u32(&ctl->q_empty), 1);
     for (int s = 0; s < NS; ++s) {
       mbar_init(smem_u32(&ctl->k_full[s]), 1);
       mbar_init(smem_u32(&ctl->k_empty[s]), 1);
@@ -514,6 +548,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(smem_u32(&ctl->p_ready[w]), kTile);
       mbar_init(smem_u32(&ctl->o_full[w]), 1);
       mbar_init(smem_u32(&ctl->o_free[w]), kTile);
+      mbar_init(smem_u32(&ctl->info_full[w]), 1);
+      mbar_init(smem_u32(&ctl->info_empty[w]), kInfoConsumers);
     }
     mbar_init_fence();
     tma_prefetch_desc(&map_q);
@@ -526,44 +562,82 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     tmem_relinquish();
   }
   fill_bias_operands(bias_a, bias_b);
-  scan_mask(ctl, p.mask + static_cast<int64_t>(batch) * p.S, p.S, n_tiles);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctl->tmem_base);
-  const int n_live = ctl->n_live;
   volatile int* abort_flag = &ctl->abort;
 
+  // Every role walks the same unit sequence; `it` counts this CTA's units, info buffer = it & 1, and the
+  // phase of an info barrier for unit `it` is (it >> 1) & 1.
   if (warp < 8) {
     // ------------------------------------------------------------------ softmax groups
     setmaxnreg_inc<kRegsSoftmax>();
     const int w = warp >> 2;
-    if (w < nq) {
-      const int row_in_tile = (warp & 3) * 32 + lane;
-      softmax_rows<D>(p, ctl, w, tmem_base, q_row0 + w * kTile + row_in_tile, bh_local);
+    const int row_in_tile = (warp & 3) * 32 + lane;
+    uint32_t tiles_done = 0;
+    int it = 0;
+    for (int u = first_unit; u < p.n_units; u += unit_step, ++it) {
+      const int buf = it & 1;
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it >> 1) & 1), abort_flag))) {
+        raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_INFO, it);
+        break;
+      }
+      const UnitGeom g = unit_geom(p, u);
+      const UnitInfo* info = &ctl->info[buf];
+      bool ok = true;
+      if (w < g.nq) {
+        ok = softmax_unit<D>(p, ctl, info, w, tmem_base, g.q_row0 + w * kTile + row_in_tile, g.bh_local, tiles_done);
+        tiles_done += static_cast<uint32_t>(info->n_live);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->info_empty[buf]));     // this warp is done with the unit's mask information
+      if (!ok) break;
     }
   } else {
     setmaxnreg_dec<kRegsOther>();
     if (warp == kWarpLoad) {
       // ---------------------------------------------------------------- loader
-      if (lane == 0 && n_live > 0) {
-        const uint32_t bar_q = smem_u32(&ctl->q_full);
-        mbar_arrive_expect_tx(bar_q, static_cast<uint32_t>(nq * Cfg::kTileBytes));
-        for (int w = 0; w < nq; ++w) tma_load_3d(q_smem + w * Cfg::kTileBytes, &map_q, bar_q, 0, q_row0 + w * kTile, bh_local);
+      if (lane == 0) {
+        uint32_t kv_done = 0;      // key tiles loaded in earlier units: ring position and phase continue across units
+        uint32_t q_loads = 0;      // units with at least one live tile so far (phase of q_full / q_empty)
         bool ok = true;
-        for (int j = 0; j < n_live && ok; ++j) {
-          const int t = ctl->live[j];
-          const int s = j % NS, round = j / NS;
-          if (round > 0 && !mbar_wait(smem_u32(&ctl->k_empty[s]), static_cast<uint32_t>((round - 1) & 1), abort_flag)) {
-            raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_FREE, j); ok = false; break;
+        int it = 0;
+        for (int u = first_unit; u < p.n_units && ok; u += unit_step, ++it) {
+          const int buf = it & 1;
+          if (!mbar_wait(smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it >> 1) & 1), abort_flag)) {
+            raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_INFO, it); ok = false; break;
           }
-          mbar_arrive_expect_tx(smem_u32(&ctl->k_full[s]), Cfg::kTileBytes);
-          tma_load_3d(k_smem + s * Cfg::kTileBytes, &map_k, smem_u32(&ctl->k_full[s]), 0, t * kTile, bh_local);
-          if (round > 0 && !mbar_wait(smem_u32(&ctl->v_empty[s]), static_cast<uint32_t>((round - 1) & 1), abort_flag)) {
-            raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_V_FREE, j); ok = false; break;
+          const UnitGeom g = unit_geom(p, u);
+          const UnitInfo* info = &ctl->info[buf];
+          const int n_live = info->n_live;
+          if (n_live > 0) {
+            // the Q tiles of the previous unit are free once its last S = Q.K^T has completed
+            if (q_loads > 0 && !mbar_wait(smem_u32(&ctl->q_empty), (q_loads - 1) & 1u, abort_flag)) {
+              raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_FREE, it); ok = false; break;
+            }
+            const uint32_t bar_q = smem_u32(&ctl->q_full);
+            mbar_arrive_expect_tx(bar_q, static_cast<uint32_t>(g.nq * Cfg::kTileBytes));
+            for (int w = 0; w < g.nq; ++w) tma_load_3d(q_smem + w * Cfg::kTileBytes, &map_q, bar_q, 0, g.q_row0 + w * kTile, g.bh_local);
+            for (int j = 0; j < n_live; ++j) {
+              const int t = info->live[j];
+              const uint32_t gidx = kv_done + static_cast<uint32_t>(j);
+              const uint32_t s = gidx % NS, round = gidx / NS;
+              if (round > 0 && !mbar_wait(smem_u32(&ctl->k_empty[s]), (round - 1) & 1u, abort_flag)) {
+                raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_FREE, j); ok = false; break;
+              }
+              mbar_arrive_expect_tx(smem_u32(&ctl->k_full[s]), Cfg::kTileBytes);
+              tma_load_3d(k_smem + s * Cfg::kTileBytes, &map_k, smem_u32(&ctl->k_full[s]), 0, t * kTile, g.bh_local);
+              if (round > 0 && !mbar_wait(smem_u32(&ctl->v_empty[s]), (round - 1) & 1u, abort_flag)) {
+                raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_V_FREE, j); ok = false; break;
+              }
+              mbar_arrive_expect_tx(smem_u32(&ctl->v_full[s]), Cfg::kTileBytes);
+              tma_load_3d(v_smem + s * Cfg::kTileBytes, &map_v, smem_u32(&ctl->v_full[s]), 0, t * kTile, g.bh_local);
+            }
+            kv_done += static_cast<uint32_t>(n_live);
+            ++q_loads;
           }
-          mbar_arrive_expect_tx(smem_u32(&ctl->v_full[s]), Cfg::kTileBytes);
-          tma_load_3d(v_smem + s * Cfg::kTileBytes, &map_v, smem_u32(&ctl->v_full[s]), 0, t * kTile, bh_local);
+          mbar_arrive(smem_u32(&ctl->info_empty[buf]));
         }
         if (!ok) {
           // unwinding: let copies that are still in flight land before the CTA may exit
@@ -573,15 +647,14 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
     } else if (warp == kWarpMma) {
       // ---------------------------------------------------------------- MMA issuer
-      if (lane == 0 && n_live > 0) {
+      if (lane == 0) {
         constexpr uint32_t idesc_s = make_idesc_i8(kTile, false);   // S = Q.K^T : N = 128 keys, both K-major
         constexpr uint32_t idesc_o = make_idesc_i8(D, true);        // O = P.V   : N = D, V is MN-major
         constexpr uint32_t idesc_bias_s = make_idesc_f16(kTile);
         constexpr uint32_t idesc_bias_o = make_idesc_f16(D);
         const uint64_t d_bias_a = make_smem_desc_noswizzle(smem_u32(bias_a), 128, 256);
         const uint64_t d_bias_b = make_smem_desc_noswizzle(smem_u32(bias_b), 128, 256);
-        bool ok = true;
-        auto issue_s = [&](int w, int stage) {
+        auto issue_s = [&](int w, uint32_t stage) {
           const uint64_t dq = make_smem_desc(q_smem + w * Cfg::kTileBytes, D);
           const uint64_t dk = make_smem_desc(k_smem + stage * Cfg::kTileBytes, D);
           mma_f16_ss(tmem_base + w * kTile, d_bias_a, d_bias_b, idesc_bias_s, 0u);      // accumulator := 0x4B400000
@@ -590,7 +663,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             mma_i8_ss(tmem_base + w * kTile, desc_advance(dq, kk * 32), desc_advance(dk, kk * 32), idesc_s, 1u);
           mma_commit(smem_u32(&ctl->s_full[w]));
         };
-        auto issue_o = [&](int w, int stage) {
+        auto issue_o = [&](int w, uint32_t stage) {
           const uint64_t dv = make_smem_desc(v_smem + stage * Cfg::kTileBytes, D);
           mma_f16_ss(tmem_base + 2 * kTile + w * D, d_bias_a, d_bias_b, idesc_bias_o, 0u);
 #pragma unroll
@@ -598,44 +671,83 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             mma_i8_ts(tmem_base + 2 * kTile + w * D, tmem_base + w * kTile + kk * 8, desc_advance(dv, kk * 32 * D), idesc_o, 1u);
           mma_commit(smem_u32(&ctl->o_full[w]));
         };
-        do {
-          if (!mbar_wait(smem_u32(&ctl->q_full), 0u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_Q_LOAD, 0); ok = false; break; }
-          if (!mbar_wait(smem_u32(&ctl->k_full[0]), 0u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_LOAD, 0); ok = false; break; }
-          tc_fence_after();
-          for (int w = 0; w < nq; ++w) issue_s(w, 0);
-          mma_commit(smem_u32(&ctl->k_empty[0]));
-          for (int j = 0; j < n_live && ok; ++j) {
-            const int s = j % NS;
-            const uint32_t ph = static_cast<uint32_t>(j & 1);
-            if (!mbar_wait(smem_u32(&ctl->v_full[s]), static_cast<uint32_t>((j / NS) & 1), abort_flag)) {
-              raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_V_LOAD, j); ok = false; break;
-            }
-            const int jn = j + 1, sn = jn % NS;
-            for (int w = 0; w < nq; ++w) {
-              if (!mbar_wait(smem_u32(&ctl->p_ready[w]), ph, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_P_READY, j); ok = false; break; }
-              if (j > 0 && !mbar_wait(smem_u32(&ctl->o_free[w]), ph ^ 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_O_FREE, j); ok = false; break; }
+        uint32_t kv_done = 0;              // key tiles consumed in earlier units (ring position / phase)
+        uint32_t tiles_done[2] = {0u, 0u}; // key tiles each query-tile slot has processed in earlier units
+        uint32_t q_loads = 0;              // units with at least one live tile seen so far (phase of q_full / q_empty)
+        bool ok = true;
+        int it = 0;
+        for (int u = first_unit; u < p.n_units && ok; u += unit_step, ++it) {
+          const int buf = it & 1;
+          if (!mbar_wait(smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it >> 1) & 1), abort_flag)) {
+            raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_INFO, it); ok = false; break;
+          }
+          const UnitGeom g = unit_geom(p, u);
+          const int n_live = ctl->info[buf].n_live;
+          const int nq = g.nq;
+          if (n_live > 0) {
+            if (!mbar_wait(smem_u32(&ctl->q_full), q_loads & 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_Q_LOAD, it); ok = false; break; }
+            {
+              const uint32_t s0 = kv_done % NS;
+              if (!mbar_wait(smem_u32(&ctl->k_full[s0]), (kv_done / NS) & 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_LOAD, 0); ok = false; break; }
               tc_fence_after();
-              FMHA_STAMP(8 + w * 2, j);
-              issue_o(w, s);
-              if (w == nq - 1) mma_commit(smem_u32(&ctl->v_empty[s]));
-              if (jn < n_live) {
-                if (w == 0 && !mbar_wait(smem_u32(&ctl->k_full[sn]), static_cast<uint32_t>((jn / NS) & 1), abort_flag)) {
-                  raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_LOAD, jn); ok = false; break;
-                }
+              for (int w = 0; w < nq; ++w) issue_s(w, s0);
+              mma_commit(smem_u32(&ctl->k_empty[s0]));
+              if (n_live == 1) mma_commit(smem_u32(&ctl->q_empty));
+            }
+            for (int j = 0; j < n_live && ok; ++j) {
+              const uint32_t gidx = kv_done + static_cast<uint32_t>(j);
+              const uint32_t s = gidx % NS;
+              if (!mbar_wait(smem_u32(&ctl->v_full[s]), (gidx / NS) & 1u, abort_flag)) {
+                raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_V_LOAD, j); ok = false; break;
+              }
+              const uint32_t gn = gidx + 1, sn = gn % NS;
+              for (int w = 0; w < nq; ++w) {
+                const uint32_t tw = tiles_done[w] + static_cast<uint32_t>(j);     // this slot's cumulative tile index
+                if (!mbar_wait(smem_u32(&ctl->p_ready[w]), tw & 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_P_READY, j); ok = false; break; }
+                if (tw > 0 && !mbar_wait(smem_u32(&ctl->o_free[w]), (tw - 1) & 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_O_FREE, j); ok = false; break; }
                 tc_fence_after();
-                // S_w / P_w columns are free again: the tensor pipe runs this thread's MMAs in order
-                FMHA_STAMP(9 + w * 2, j);
-                issue_s(w, sn);
-                if (w == nq - 1) mma_commit(smem_u32(&ctl->k_empty[sn]));
+                issue_o(w, s);
+                if (w == nq - 1) mma_commit(smem_u32(&ctl->v_empty[s]));
+                if (j + 1 < n_live) {
+                  if (w == 0 && !mbar_wait(smem_u32(&ctl->k_full[sn]), (gn / NS) & 1u, abort_flag)) {
+                    raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_LOAD, j + 1); ok = false; break;
+                  }
+                  tc_fence_after();
+                  // S_w / P_w columns are free again: the tensor pipe runs this thread's MMAs in order
+                  issue_s(w, sn);
+                  if (w == nq - 1) {
+                    mma_commit(smem_u32(&ctl->k_empty[sn]));
+                    if (j + 2 == n_live) mma_commit(smem_u32(&ctl->q_empty));    // that was the unit's last use of Q
+                  }
+                }
               }
             }
+            kv_done += static_cast<uint32_t>(n_live);
+            for (int w = 0; w < nq; ++w) tiles_done[w] += static_cast<uint32_t>(n_live);
+            ++q_loads;
           }
-        } while (false);
+          mbar_arrive(smem_u32(&ctl->info_empty[buf]));
+        }
+      }
+    } else if (warp == kWarpScan) {
+      // ---------------------------------------------------------------- scanner: mask information, one unit ahead
+      bool ok = true;
+      int it = 0;
+      for (int u = first_unit; u < p.n_units && ok; u += unit_step, ++it) {
+        const int buf = it & 1;
+        // the buffer was used by unit it-2: wait until all ten consumer warps have released it
+        if (it >= 2) {
+          ok = __all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&ctl->info_empty[buf]), static_cast<uint32_t>(((it >> 1) - 1) & 1), abort_flag));
+          if (!ok) { if (lane == 0) raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_INFO, it); break; }
+        }
+        const UnitGeom g = unit_geom(p, u);
+        scan_mask_warp(&ctl->info[buf], p.mask + static_cast<int64_t>(g.batch) * p.S, p.S, n_tiles);
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->info_full[buf]));
       }
     }
   }
 
-  // everything this CTA issued has been consumed by the time the softmax groups leave their loop
+  // every unit of this CTA has been computed and stored by the time the softmax groups leave their loop
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
