@@ -35,7 +35,8 @@ enum {
   FMHA_I8_ERR_BAD_SLICE = -8,      /* bh_begin/bh_count outside [0, B*H] */
   FMHA_I8_ERR_BAD_AMAX = -9,       /* an amax is not a finite positive number */
   FMHA_I8_ERR_TOO_LARGE = -10,     /* size beyond a stated maximum of the entry point */
-  FMHA_I8_ERR_DEVICE = -11         /* the device status words are non-zero (see device_status) */
+  FMHA_I8_ERR_DEVICE = -11,        /* the device status words are non-zero (see device_status) */
+  FMHA_I8_ERR_BAD_FLAGS = -12      /* a flag bit this library does not define is set */
 };
 
 /* words[0] of fmha_i8_sm100_device_status(): the bounded wait that ran out first. */
@@ -55,6 +56,10 @@ enum {
 };
 
 #define FMHA_I8_FLAG_USE_TCU 1u    /* mirrors the reference's use_tcu argument; must be set */
+/* P quantised as UNSIGNED 8 bit with 255 levels, P8 = rn(255 p), final scale v_amax/(255 o_amax): the
+ * UINT8 x INT8 variant the reference's README lists as planned (README.md:15,137-143,186) and its kernel
+ * does not have.  Off by default: without it P8 = -rn(128 p) as in inc/fmha_i8.cuh:241-250. */
+#define FMHA_I8_FLAG_UINT8_P 2u
 
 /* Replaces gpuImpl::FMHAInferI8 / LaunchFMHAInfer_TCU / FMHAInferKernel
  * (src/fmha_i8.cu:157-173, :31-155, inc/fmha_i8.cuh:43-334): the whole forward pass
@@ -68,6 +73,17 @@ int fmha_i8_sm100_infer(void* stream, const float amax[5], const int desc[4],
  * slice (each GPU holds only its slice); mask is the whole [B,S] mask and desc the whole shape.
  * The reference has no counterpart: its grid is (batch, head) on one GPU (src/fmha_i8.cu:43). */
 int fmha_i8_sm100_infer_slice(void* stream, const float amax[5], const int desc[4],
+                              const void* q, const void* k, const void* v, const void* mask, void* o,
+                              int bh_begin, int bh_count, unsigned flags);
+
+/* Attention with a different number of query rows and keys (cross-attention, decoding against a cache):
+ * desc5 = {batch_num, seq_len_q, seq_len_k, head_num, head_dim}; q and o are int8 [B,H,seq_len_q,D],
+ * k and v int8 [B,H,seq_len_k,D], mask int8 [B,seq_len_k].  seq_len_q is any number from 1 to 32768,
+ * seq_len_k a multiple of 64 up to 32768.  bh_begin/bh_count select heads as in
+ * fmha_i8_sm100_infer_slice (0 and B*H for the whole problem).  The reference lists this shape as
+ * planned (README.md:13) and has no entry point for it; its CPU softmax already takes both lengths
+ * (inc/cpuSoftmax.hpp:12), which is what the test oracle is pinned to. */
+int fmha_i8_sm100_infer_cross(void* stream, const float amax[5], const int desc5[5],
                               const void* q, const void* k, const void* v, const void* mask, void* o,
                               int bh_begin, int bh_count, unsigned flags);
 
@@ -96,6 +112,12 @@ int fmha_i8_sm100_debug_pv(void* stream, const int desc[4], const void* p, const
  * selected by the product entry points.  Same arguments as fmha_i8_sm100_infer. */
 int fmha_i8_sm100_debug_simt(void* stream, const float amax[5], const int desc[4],
                              const void* q, const void* k, const void* v, const void* mask, void* o);
+
+/* The same cross-check for the extended shapes and flags of fmha_i8_sm100_infer_cross
+ * (desc5 = {batch_num, seq_len_q, seq_len_k, head_num, head_dim}; flags: FMHA_I8_FLAG_UINT8_P or 0). */
+int fmha_i8_sm100_debug_simt_x(void* stream, const float amax[5], const int desc5[5],
+                               const void* q, const void* k, const void* v, const void* mask, void* o,
+                               unsigned flags);
 
 /* Per-tensor symmetric quantisation on the device, the producer step in front of the attention call:
  * amax = max|x| (abs_max, inc/utils.hpp:31-39) and q[i] = clamp(floor(x[i]*127/amax + 0.5), -127, 127)

@@ -26,11 +26,13 @@ ERR_BAD_SLICE = -8
 ERR_BAD_AMAX = -9
 ERR_TOO_LARGE = -10
 ERR_DEVICE = -11
+ERR_BAD_FLAGS = -12
 FLAG_USE_TCU = 1
+FLAG_UINT8_P = 2     # P quantised as unsigned 8 bit, 255 levels (the reference README's planned variant)
 
 EXPORTS = (
-    "fmha_i8_sm100_infer", "fmha_i8_sm100_infer_slice", "fmha_i8_sm100_infer_host",
-    "fmha_i8_sm100_debug_qk", "fmha_i8_sm100_debug_pv", "fmha_i8_sm100_debug_simt",
+    "fmha_i8_sm100_infer", "fmha_i8_sm100_infer_slice", "fmha_i8_sm100_infer_cross", "fmha_i8_sm100_infer_host",
+    "fmha_i8_sm100_debug_qk", "fmha_i8_sm100_debug_pv", "fmha_i8_sm100_debug_simt", "fmha_i8_sm100_debug_simt_x",
     "fmha_i8_sm100_quantize_f32", "fmha_i8_sm100_quantize_f32_noalloc", "fmha_i8_sm100_device_status", "fmha_i8_sm100_last_status", "fmha_i8_sm100_status_string",
     "fmha_i8_sm100_launch_count", "fmha_i8_sm100_version",
 )
@@ -52,6 +54,19 @@ class AttnDataDescriptor:
 
     def as_c(self):
         return (ctypes.c_int * 4)(self.batch_num, self.seq_len, self.head_num, self.head_dim)
+
+
+@dataclass
+class AttnDataDescriptorX:
+    """Shape with separate query and key lengths (the reference lists this as planned, README.md:13)."""
+    batch_num: int = 1
+    seq_len_q: int = 64
+    seq_len_k: int = 64
+    head_num: int = 4
+    head_dim: int = 64
+
+    def as_c(self):
+        return (ctypes.c_int * 5)(self.batch_num, self.seq_len_q, self.seq_len_k, self.head_num, self.head_dim)
 
 
 @dataclass
@@ -81,10 +96,12 @@ def lib():
         vp, fp, ip, u = ctypes.c_void_p, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_int), ctypes.c_uint
         L.fmha_i8_sm100_infer.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, u]
         L.fmha_i8_sm100_infer_slice.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, u]
+        L.fmha_i8_sm100_infer_cross.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, u]
         L.fmha_i8_sm100_infer_host.argtypes = [fp, ip, vp, vp, vp, vp, vp, u]
         L.fmha_i8_sm100_debug_qk.argtypes = [vp, ip, vp, vp, vp]
         L.fmha_i8_sm100_debug_pv.argtypes = [vp, ip, vp, vp, vp, u]
         L.fmha_i8_sm100_debug_simt.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp]
+        L.fmha_i8_sm100_debug_simt_x.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, u]
         L.fmha_i8_sm100_quantize_f32.argtypes = [vp, vp, ctypes.c_longlong, vp, vp]
         L.fmha_i8_sm100_quantize_f32_noalloc.argtypes = [vp, vp, ctypes.c_longlong, vp, vp]
         L.fmha_i8_sm100_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
@@ -123,7 +140,11 @@ def _stream_handle(stream):
     return ctypes.c_void_p(stream.cuda_stream)
 
 
-def FMHAInferI8(stream, fmha_param, attn_desc, q, k, v, padding_mask, o, use_tcu=True, check=True):
+def _flags(use_tcu=True, uint8_p=False):
+    return (FLAG_USE_TCU if use_tcu else 0) | (FLAG_UINT8_P if uint8_p else 0)
+
+
+def FMHAInferI8(stream, fmha_param, attn_desc, q, k, v, padding_mask, o, use_tcu=True, check=True, uint8_p=False):
     """Mirror of gpuImpl::FMHAInferI8 (reference inc/fmha_i8.h:7-15).
 
     q, k, v, o: int8 [B,H,S,D] device tensors; padding_mask: int8 [B,S], non-zero = key masked.
@@ -131,25 +152,39 @@ def FMHAInferI8(stream, fmha_param, attn_desc, q, k, v, padding_mask, o, use_tcu
     synchronising.  With check=True a non-zero status raises FmhaError (the reference returns void
     and silently does nothing on unsupported input)."""
     st = lib().fmha_i8_sm100_infer(_stream_handle(stream), fmha_param.as_c(), attn_desc.as_c(), _ptr(q), _ptr(k),
-                                   _ptr(v), _ptr(padding_mask), _ptr(o), FLAG_USE_TCU if use_tcu else 0)
+                                   _ptr(v), _ptr(padding_mask), _ptr(o), _flags(use_tcu, uint8_p))
     if check and st != OK:
         raise FmhaError(st, "FMHAInferI8")
     return st
 
 
-def FMHAInferI8Slice(stream, fmha_param, attn_desc, q, k, v, padding_mask, o, bh_begin, bh_count, check=True):
+def FMHAInferI8Cross(stream, fmha_param, attn_desc_x, q, k, v, padding_mask, o, bh_begin=0, bh_count=None,
+                     use_tcu=True, check=True, uint8_p=False):
+    """Query rows and keys differ in number: q, o int8 [B,H,Sq,D]; k, v int8 [B,H,Sk,D]; padding_mask int8
+    [B,Sk].  attn_desc_x is an AttnDataDescriptorX.  bh_begin/bh_count select heads as in FMHAInferI8Slice."""
+    if bh_count is None:
+        bh_count = attn_desc_x.batch_num * attn_desc_x.head_num - bh_begin
+    st = lib().fmha_i8_sm100_infer_cross(_stream_handle(stream), fmha_param.as_c(), attn_desc_x.as_c(), _ptr(q), _ptr(k),
+                                         _ptr(v), _ptr(padding_mask), _ptr(o), int(bh_begin), int(bh_count),
+                                         _flags(use_tcu, uint8_p))
+    if check and st != OK:
+        raise FmhaError(st, "FMHAInferI8Cross")
+    return st
+
+
+def FMHAInferI8Slice(stream, fmha_param, attn_desc, q, k, v, padding_mask, o, bh_begin, bh_count, check=True, uint8_p=False):
     """Heads [bh_begin, bh_begin+bh_count) of the flattened batch*head axis; q,k,v,o hold only the slice."""
     st = lib().fmha_i8_sm100_infer_slice(_stream_handle(stream), fmha_param.as_c(), attn_desc.as_c(), _ptr(q), _ptr(k),
-                                         _ptr(v), _ptr(padding_mask), _ptr(o), int(bh_begin), int(bh_count), FLAG_USE_TCU)
+                                         _ptr(v), _ptr(padding_mask), _ptr(o), int(bh_begin), int(bh_count), _flags(True, uint8_p))
     if check and st != OK:
         raise FmhaError(st, "FMHAInferI8Slice")
     return st
 
 
-def FMHAInferI8Host(fmha_param, attn_desc, host_q, host_k, host_v, host_mask, host_o, check=True):
+def FMHAInferI8Host(fmha_param, attn_desc, host_q, host_k, host_v, host_mask, host_o, check=True, uint8_p=False):
     """Host buffers in, host buffer out (copies inside); synchronous."""
     st = lib().fmha_i8_sm100_infer_host(fmha_param.as_c(), attn_desc.as_c(), _ptr(host_q), _ptr(host_k), _ptr(host_v),
-                                        _ptr(host_mask), _ptr(host_o), FLAG_USE_TCU)
+                                        _ptr(host_mask), _ptr(host_o), _flags(True, uint8_p))
     if check and st != OK:
         raise FmhaError(st, "FMHAInferI8Host")
     return st
@@ -172,6 +207,13 @@ def debug_simt(stream, fmha_param, attn_desc, q, k, v, padding_mask, o):
                                         _ptr(v), _ptr(padding_mask), _ptr(o))
     if st != OK:
         raise FmhaError(st, "debug_simt")
+
+
+def debug_simt_x(stream, fmha_param, attn_desc_x, q, k, v, padding_mask, o, uint8_p=False):
+    st = lib().fmha_i8_sm100_debug_simt_x(_stream_handle(stream), fmha_param.as_c(), attn_desc_x.as_c(), _ptr(q), _ptr(k),
+                                          _ptr(v), _ptr(padding_mask), _ptr(o), FLAG_UINT8_P if uint8_p else 0)
+    if st != OK:
+        raise FmhaError(st, "debug_simt_x")
 
 
 def quantize_f32(stream, x, out, amax_out=None, n=None, entry="fmha_i8_sm100_quantize_f32"):

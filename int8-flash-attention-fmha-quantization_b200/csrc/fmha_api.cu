@@ -135,12 +135,22 @@ int make_map(CUtensorMap* map, const void* base, int n_heads, int S, int D) {
 
 bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
-int check_shape(const int desc[4]) {
-  const int B = desc[0], S = desc[1], H = desc[2], D = desc[3];
-  if (B < 1 || H < 1 || S < 64 || S > kMaxSeq || (S % 64) != 0) return FMHA_I8_ERR_BAD_SHAPE;
-  if (D != 64 && D != 128) return FMHA_I8_ERR_BAD_SHAPE;
-  if (static_cast<long long>(B) * H > 0x7FFFFFFFLL / 2) return FMHA_I8_ERR_BAD_SHAPE;
+// Shape as the kernel sees it: Sq query rows and Sk keys per head (equal for the reference's self-attention).
+struct Shape {
+  int B, Sq, Sk, H, D;
+};
+
+int check_shape_x(const Shape& sh) {
+  if (sh.B < 1 || sh.H < 1 || sh.Sk < 64 || sh.Sk > kMaxSeq || (sh.Sk % 64) != 0) return FMHA_I8_ERR_BAD_SHAPE;
+  if (sh.Sq < 1 || sh.Sq > kMaxSeq) return FMHA_I8_ERR_BAD_SHAPE;
+  if (sh.D != 64 && sh.D != 128) return FMHA_I8_ERR_BAD_SHAPE;
+  if (static_cast<long long>(sh.B) * sh.H > 0x7FFFFFFFLL / 2) return FMHA_I8_ERR_BAD_SHAPE;
   return FMHA_I8_OK;
+}
+
+int check_shape(const int desc[4]) {
+  const Shape sh{desc[0], desc[1], desc[1], desc[2], desc[3]};
+  return check_shape_x(sh);
 }
 
 // The reference evaluates 1/sqrt(head_dim) with a Newton iteration carried in float
@@ -156,12 +166,16 @@ float reference_row_scale(int D) {
   return 1.0f / curr;
 }
 
-int fill_params(FwdParams* p, const float amax[5], const int desc[4]) {
+int fill_params(FwdParams* p, const float amax[5], int D, unsigned flags = 0u) {
   for (int i = 0; i < 4; ++i)
     if (!(amax[i] > 0.f) || !std::isfinite(amax[i])) return FMHA_I8_ERR_BAD_AMAX;
-  p->row_scale = reference_row_scale(desc[3]);
+  const bool up = (flags & FMHA_I8_FLAG_UINT8_P) != 0u;
+  p->row_scale = reference_row_scale(D);
   p->scale_qk = amax[0] * amax[1] / (127.f * 127.f);
-  p->scale_v_out = amax[2] * (1.0f / (amax[3] * 128.f));
+  p->scale_v_out = amax[2] * (1.0f / (amax[3] * (up ? 255.f : 128.f)));
+  p->p_mul = up ? 255.f : -128.f;
+  p->o_sign = up ? 1.f : -1.f;
+  p->p_unsigned = up ? 1u : 0u;
   p->c2 = static_cast<float>(static_cast<double>(p->row_scale) * static_cast<double>(p->scale_qk) * 1.4426950408889634);
   if (!(p->c2 > 0.f) || !std::isfinite(p->c2 * kMagic)) return FMHA_I8_ERR_BAD_AMAX;
   return FMHA_I8_OK;
@@ -171,7 +185,7 @@ template <int D>
 int launch_fwd(cudaStream_t stream, DeviceInfo* dev, FwdParams p, const void* q, const void* k, const void* v) {
   CUtensorMap mq, mk, mv;
   int st;
-  if ((st = make_map(&mq, q, p.bh_count, p.S, D)) != FMHA_I8_OK) return st;
+  if ((st = make_map(&mq, q, p.bh_count, p.Sq, D)) != FMHA_I8_OK) return st;
   if ((st = make_map(&mk, k, p.bh_count, p.S, D)) != FMHA_I8_OK) return st;
   if ((st = make_map(&mv, v, p.bh_count, p.S, D)) != FMHA_I8_OK) return st;
   // persistent CTAs: one per SM (tensor memory is allocated whole), each walking its share of the units
@@ -181,29 +195,31 @@ int launch_fwd(cudaStream_t stream, DeviceInfo* dev, FwdParams p, const void* q,
   return cudaGetLastError() == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH;
 }
 
-int infer_slice_impl(void* stream, const float amax[5], const int desc[4], const void* q, const void* k,
-                     const void* v, const void* mask, void* o, int bh_begin, int bh_count, unsigned flags) {
-  if (!amax || !desc || !q || !k || !v || !mask || !o) return FMHA_I8_ERR_NULL_POINTER;
+int infer_x_impl(void* stream, const float amax[5], const Shape& sh, const void* q, const void* k,
+                 const void* v, const void* mask, void* o, int bh_begin, int bh_count, unsigned flags) {
+  if (!amax || !q || !k || !v || !mask || !o) return FMHA_I8_ERR_NULL_POINTER;
   if (!(flags & FMHA_I8_FLAG_USE_TCU)) return FMHA_I8_ERR_NO_CUDA_CORE_PATH;
-  int st = check_shape(desc);
+  if (flags & ~(FMHA_I8_FLAG_USE_TCU | FMHA_I8_FLAG_UINT8_P)) return FMHA_I8_ERR_BAD_FLAGS;
+  int st = check_shape_x(sh);
   if (st != FMHA_I8_OK) return st;
-  const long long BH = static_cast<long long>(desc[0]) * desc[2];
+  const long long BH = static_cast<long long>(sh.B) * sh.H;
   if (bh_begin < 0 || bh_count < 1 || static_cast<long long>(bh_begin) + bh_count > BH) return FMHA_I8_ERR_BAD_SLICE;
   if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(o, 16) || !aligned(mask, 4))
     return FMHA_I8_ERR_MISALIGNED;
   FwdParams p{};
-  if ((st = fill_params(&p, amax, desc)) != FMHA_I8_OK) return st;
+  if ((st = fill_params(&p, amax, sh.D, flags)) != FMHA_I8_OK) return st;
   int err = FMHA_I8_OK;
   DeviceInfo* dev = current_device(&err);
   if (!dev) return err;
   if ((st = set_kernel_attributes(dev)) != FMHA_I8_OK) return st;
   p.mask = static_cast<const int8_t*>(mask);
   p.o = static_cast<int8_t*>(o);
-  p.S = desc[1];
-  p.H = desc[2];
+  p.S = sh.Sk;
+  p.Sq = sh.Sq;
+  p.H = sh.H;
   p.bh_begin = bh_begin;
   p.bh_count = bh_count;
-  p.q_pairs = (p.S + 2 * kTile - 1) / (2 * kTile);
+  p.q_pairs = (p.Sq + 2 * kTile - 1) / (2 * kTile);
   {
     const long long units = static_cast<long long>(bh_count) * p.q_pairs;
     if (units > 0x7FFFFFFFLL) return FMHA_I8_ERR_BAD_SHAPE;
@@ -211,7 +227,14 @@ int infer_slice_impl(void* stream, const float amax[5], const int desc[4], const
   }
   p.status = dev->status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return desc[3] == 128 ? launch_fwd<128>(s, dev, p, q, k, v) : launch_fwd<64>(s, dev, p, q, k, v);
+  return sh.D == 128 ? launch_fwd<128>(s, dev, p, q, k, v) : launch_fwd<64>(s, dev, p, q, k, v);
+}
+
+int infer_slice_impl(void* stream, const float amax[5], const int desc[4], const void* q, const void* k,
+                     const void* v, const void* mask, void* o, int bh_begin, int bh_count, unsigned flags) {
+  if (!desc) return FMHA_I8_ERR_NULL_POINTER;
+  const Shape sh{desc[0], desc[1], desc[1], desc[2], desc[3]};
+  return infer_x_impl(stream, amax, sh, q, k, v, mask, o, bh_begin, bh_count, flags);
 }
 
 // Device staging buffers of fmha_i8_sm100_infer_host, one set per device, grown on demand, plus the
@@ -273,6 +296,13 @@ int fmha_i8_sm100_infer(void* stream, const float amax[5], const int desc[4], co
 int fmha_i8_sm100_infer_slice(void* stream, const float amax[5], const int desc[4], const void* q, const void* k,
                               const void* v, const void* mask, void* o, int bh_begin, int bh_count, unsigned flags) {
   return finish(infer_slice_impl(stream, amax, desc, q, k, v, mask, o, bh_begin, bh_count, flags));
+}
+
+int fmha_i8_sm100_infer_cross(void* stream, const float amax[5], const int desc5[5], const void* q, const void* k,
+                              const void* v, const void* mask, void* o, int bh_begin, int bh_count, unsigned flags) {
+  if (!desc5) return finish(FMHA_I8_ERR_NULL_POINTER);
+  const Shape sh{desc5[0], desc5[1], desc5[2], desc5[3], desc5[4]};
+  return finish(infer_x_impl(stream, amax, sh, q, k, v, mask, o, bh_begin, bh_count, flags));
 }
 
 int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void* host_q, const void* host_k,
@@ -402,29 +432,39 @@ int fmha_i8_sm100_debug_pv(void* stream, const int desc[4], const void* p, const
   return finish(cudaGetLastError() == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH);
 }
 
-int fmha_i8_sm100_debug_simt(void* stream, const float amax[5], const int desc[4], const void* q, const void* k,
-                             const void* v, const void* mask, void* o) {
-  if (!amax || !desc || !q || !k || !v || !mask || !o) return finish(FMHA_I8_ERR_NULL_POINTER);
-  int st = check_shape(desc);
+int fmha_i8_sm100_debug_simt_x(void* stream, const float amax[5], const int desc5[5], const void* q, const void* k,
+                               const void* v, const void* mask, void* o, unsigned flags) {
+  if (!amax || !desc5 || !q || !k || !v || !mask || !o) return finish(FMHA_I8_ERR_NULL_POINTER);
+  const Shape sh{desc5[0], desc5[1], desc5[2], desc5[3], desc5[4]};
+  int st = check_shape_x(sh);
   if (st != FMHA_I8_OK) return finish(st);
   if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(o, 16)) return finish(FMHA_I8_ERR_MISALIGNED);
   FwdParams p{};
-  if ((st = fill_params(&p, amax, desc)) != FMHA_I8_OK) return finish(st);
+  if ((st = fill_params(&p, amax, sh.D, flags)) != FMHA_I8_OK) return finish(st);
   int err = FMHA_I8_OK;
   if (!current_device(&err)) return finish(err);
-  const int BH = desc[0] * desc[2], S = desc[1], H = desc[2], D = desc[3];
+  const long long BH = static_cast<long long>(sh.B) * sh.H;
   if (BH > 65535) return finish(FMHA_I8_ERR_TOO_LARGE);
-  const dim3 grid((S + kTile - 1) / kTile, BH);
+  const dim3 grid((sh.Sq + kTile - 1) / kTile, static_cast<unsigned>(BH));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int8_t* q8 = static_cast<const int8_t*>(q);
   const int8_t* k8 = static_cast<const int8_t*>(k);
   const int8_t* v8 = static_cast<const int8_t*>(v);
   const int8_t* m8 = static_cast<const int8_t*>(mask);
   int8_t* o8 = static_cast<int8_t*>(o);
-  if (D == 128) simt_check_kernel<128><<<grid, 128, 0, s>>>(q8, k8, v8, m8, o8, S, H, 0, p.row_scale, p.scale_qk, p.scale_v_out);
-  else simt_check_kernel<64><<<grid, 128, 0, s>>>(q8, k8, v8, m8, o8, S, H, 0, p.row_scale, p.scale_qk, p.scale_v_out);
+  if (sh.D == 128)
+    simt_check_kernel<128><<<grid, 128, 0, s>>>(q8, k8, v8, m8, o8, sh.Sq, sh.Sk, sh.H, 0, p.row_scale, p.scale_qk, p.scale_v_out, p.p_mul, p.o_sign);
+  else
+    simt_check_kernel<64><<<grid, 128, 0, s>>>(q8, k8, v8, m8, o8, sh.Sq, sh.Sk, sh.H, 0, p.row_scale, p.scale_qk, p.scale_v_out, p.p_mul, p.o_sign);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
   return finish(cudaGetLastError() == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH);
+}
+
+int fmha_i8_sm100_debug_simt(void* stream, const float amax[5], const int desc[4], const void* q, const void* k,
+                             const void* v, const void* mask, void* o) {
+  if (!desc) return finish(FMHA_I8_ERR_NULL_POINTER);
+  const int desc5[5] = {desc[0], desc[1], desc[1], desc[2], desc[3]};
+  return fmha_i8_sm100_debug_simt_x(stream, amax, desc5, q, k, v, mask, o, 0u);
 }
 
 int fmha_i8_sm100_quantize_f32(void* stream, const float* x, long long n, int8_t* out, float* amax_out) {
@@ -510,6 +550,7 @@ const char* fmha_i8_sm100_status_string(int status) {
     case FMHA_I8_ERR_BAD_AMAX: return "amax values must be finite and positive";
     case FMHA_I8_ERR_TOO_LARGE: return "size beyond the maximum of this entry point";
     case FMHA_I8_ERR_DEVICE: return "a device-side bounded wait ran out (see fmha_i8_sm100_device_status)";
+    case FMHA_I8_ERR_BAD_FLAGS: return "an undefined flag bit is set";
     default: return "unknown status";
   }
 }

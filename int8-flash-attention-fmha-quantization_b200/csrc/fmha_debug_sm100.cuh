@@ -196,8 +196,8 @@ debug_pv_kernel(const __grid_constant__ CUtensorMap map_v, const int8_t* p8, int
 template <int D>
 __global__ void __launch_bounds__(128)
 simt_check_kernel(const int8_t* __restrict__ q, const int8_t* __restrict__ k, const int8_t* __restrict__ v,
-                  const int8_t* __restrict__ mask, int8_t* __restrict__ o, int S, int H, int bh_begin,
-                  float row_scale, float scale_qk, float scale_v_out) {
+                  const int8_t* __restrict__ mask, int8_t* __restrict__ o, int Sq, int S, int H, int bh_begin,
+                  float row_scale, float scale_qk, float scale_v_out, float p_mul, float o_sign) {
   __shared__ __align__(16) int8_t ks[kTile * D];
   __shared__ __align__(16) int8_t vs[kTile * D];
   __shared__ int8_t ms[kTile];
@@ -205,12 +205,13 @@ simt_check_kernel(const int8_t* __restrict__ q, const int8_t* __restrict__ k, co
   const int bh = blockIdx.y;
   const int row = blockIdx.x * kTile + threadIdx.x;
   const int batch = (bh_begin + bh) / H;
-  const int64_t head_off = static_cast<int64_t>(bh) * S * D;
+  const int64_t head_off = static_cast<int64_t>(bh) * S * D;       // keys and values: S rows per head
+  const int64_t q_head_off = static_cast<int64_t>(bh) * Sq * D;    // queries and output: Sq rows per head
 
   int qreg[D / 4];
 #pragma unroll
   for (int i = 0; i < D / 4; ++i)
-    qreg[i] = (row < S) ? reinterpret_cast<const int*>(q + head_off + static_cast<int64_t>(row) * D)[i] : 0;
+    qreg[i] = (row < Sq) ? reinterpret_cast<const int*>(q + q_head_off + static_cast<int64_t>(row) * D)[i] : 0;
 
   float oacc[D];
 #pragma unroll
@@ -260,7 +261,7 @@ simt_check_kernel(const int8_t* __restrict__ q, const int8_t* __restrict__ k, co
       const float sf = __fmul_rn(__fmul_rn(row_scale, static_cast<float>(s_loc[c])), scale_qk);
       const float pe = (ms[c] != 0) ? 0.f : expf(__fsub_rn(sf, m_t));
       l_t = __fadd_rn(l_t, pe);
-      const int p8 = __float2int_rn(fmaxf(fminf(__fmul_rn(-128.f, pe), 0.f), -128.f));
+      const int p8 = __float2int_rn(fmaxf(fminf(__fmul_rn(p_mul, pe), fmaxf(p_mul, 0.f)), fminf(p_mul, 0.f)));   // -rn(128 p) or rn(255 p)
       if (p8 != 0) {
         const int8_t* vr = vs + c * D;
 #pragma unroll
@@ -275,12 +276,12 @@ simt_check_kernel(const int8_t* __restrict__ q, const int8_t* __restrict__ k, co
     const float a = __fmul_rn(l_run, e_old);
 #pragma unroll
     for (int i = 0; i < D; ++i)
-      oacc[i] = __fmul_rn(rcp, __fadd_rn(__fmul_rn(a, oacc[i]), __fmul_rn(e_cur, __fmul_rn(-1.f, static_cast<float>(ot[i])))));
+      oacc[i] = __fmul_rn(rcp, __fadd_rn(__fmul_rn(a, oacc[i]), __fmul_rn(e_cur, __fmul_rn(o_sign, static_cast<float>(ot[i])))));
     l_run = l_new;
     m_run = m_new;
   }
-  if (row < S) {
-    int8_t* dst = o + head_off + static_cast<int64_t>(row) * D;
+  if (row < Sq) {
+    int8_t* dst = o + q_head_off + static_cast<int64_t>(row) * D;
 #pragma unroll
     for (int i = 0; i < D; ++i)
       dst[i] = static_cast<int8_t>(__float2int_rn(fmaxf(fminf(__fmul_rn(scale_v_out, oacc[i]), 127.f), -127.f)));

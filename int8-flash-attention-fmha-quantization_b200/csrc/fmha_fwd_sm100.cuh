@@ -4,18 +4,23 @@
 // contract -- key tiles of 128 starting at key 0, P quantised to 8 bits against each tile's own row
 // maximum, tiles merged in fp32 -- on a different machine model:
 //
-//   work unit  = (batch*head, pair of 128-row query tiles); one CTA per unit, one CTA per SM
-//   warp 8     = loader: TMA brings Q (once) and a ring of K and V tiles into swizzled shared memory
+//   work unit  = (batch*head, pair of 128-row query tiles).  The kernel is persistent: min(units, SMs)
+//                CTAs, one per SM, CTA c walks units c, c + grid, ...; barrier phases, the K/V ring and
+//                tensor memory carry on from one unit to the next.
+//   warp 8     = loader: TMA brings Q (once per unit) and a ring of K and V tiles into swizzled shared
+//                memory, running ahead into the next unit
 //   warp 9     = MMA issuer: one thread issues tcgen05.mma
 //                  S_w   = bias + Q_w . K_j^T   (smem x smem  -> int32 in tensor memory)
 //                  O~_w  = bias + P_w . V_j     (tmem x smem  -> int32 in tensor memory)
+//   warp 10    = scanner: turns the next unit's padding-mask row into per-tile bit masks and the list
+//                of key tiles that hold at least one unmasked key (double-buffered)
 //   warps 0-3  = softmax group of query tile 0, warps 4-7 = of query tile 1: one thread owns one
 //                query row, so row max / row sum need no shuffles.  Per key tile a thread reads its S
 //                row from tensor memory twice (integer max, then exp + requantise), writes the 8-bit P
 //                row back over the front of S, and after P.V drains the partial output into its fp32
 //                running row.
-//   warps 10-11 idle (they complete the third warpgroup so registers can be moved to the softmax
-//                groups with setmaxnreg).
+//   warp 11    idle (it completes the third warpgroup so registers can be moved to the softmax groups
+//                with setmaxnreg).
 //
 // The bias: every accumulator is first written by a one-step fp16 MMA whose operands hold 4096 and
 // 3072, i.e. the fp32 value 1.5*2^23 (bits 0x4B400000); the int8 MMAs then add their integer result
@@ -83,12 +88,18 @@ template <int D> struct FwdCfg {
 struct FwdParams {
   const int8_t* mask;   // [B,S] whole mask
   int8_t* o;            // first head of the slice
-  int S, H, bh_begin, bh_count, q_pairs;
+  int S;                // keys per head (seq_len; seq_len_k when queries and keys differ in number)
+  int Sq;               // query rows per head (== S for self-attention)
+  int H, bh_begin, bh_count, q_pairs;
   int n_units;          // bh_count * q_pairs work units, taken round-robin by the resident CTAs
   float row_scale;      // 1/sqrt(D), the reference's constant (inc/fmha_i8.cuh:71)
   float scale_qk;       // q_amax*k_amax/127^2 (inc/fmha_i8.cuh:72)
   float scale_v_out;    // v_amax/(o_amax*128) (inc/fmha_i8.cuh:318)
   float c2;             // row_scale*scale_qk*log2(e)
+  float p_mul;          // -128: P8 = -rn(128 p) signed, the reference's quantisation (inc/fmha_i8.cuh:241-250);
+                        // +255: P8 = rn(255 p) unsigned (the reference README's planned UINT8 x INT8 variant)
+  float o_sign;         // -1 when the accumulator holds -(P.V) (signed P), +1 when it holds +(P.V)
+  unsigned p_unsigned;  // 1 = the tensor core reads P as unsigned bytes
   unsigned* status;     // eight device status words
 };
 
@@ -299,7 +310,7 @@ struct RowConsts {
   float2 c2, neg_hi, neg_128f;
   float f, m_tile;
 };
-__device__ __forceinline__ RowConsts row_consts(const int imax, const float c2s, const float row_scale, const float scale_qk) {
+__device__ __forceinline__ RowConsts row_consts(const int imax, const float c2s, const float row_scale, const float scale_qk, const float p_mul) {
   // exponent argument (s - smax) * c2 = x * c2 - M * c2 with x = kMagic + s and M = kMagic + smax.
   // M * c2 = hi + lo exactly (lo is the rounding residual); the factor 2^-lo is folded into the
   // quantisation constant and the row sum, so nothing is lost and nothing is paid per element.
@@ -310,7 +321,7 @@ __device__ __forceinline__ RowConsts row_consts(const int imax, const float c2s,
   k.f = fmaf(-lo, 0.6931471805599453f, 1.0f);
   k.c2 = make_float2(c2s, c2s);
   k.neg_hi = make_float2(-hi, -hi);
-  k.neg_128f = make_float2(-128.f * k.f, -128.f * k.f);
+  k.neg_128f = make_float2(p_mul * k.f, p_mul * k.f);       // -128 f (or +255 f): quantisation multiplier
   // the value the reference computes for the maximal element (inc/fmha_i8.cuh:196)
   k.m_tile = (row_scale * static_cast<float>(imax - static_cast<int>(kMagicBits))) * scale_qk;
   return k;
@@ -334,7 +345,7 @@ __device__ __forceinline__ TileStats softmax_tile_fast(const uint32_t tS, const 
     tmem_ld16_issue(tS, ra);                 // first chunk of pass 2, in flight during the second half of the max
     chunk_max<false, 64>(wide, 0u, max_a, max_b);
   }
-  const RowConsts k = row_consts(max(max_a, max_b), p.c2, p.row_scale, p.scale_qk);
+  const RowConsts k = row_consts(max(max_a, max_b), p.c2, p.row_scale, p.scale_qk, p.p_mul);
   if ((threadIdx.x >> 5 & 3) == FMHA_TRACE_Q) FMHA_STAMP(trace_slot, trace_idx);
   float2 sum[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
   uint32_t packed[4];
@@ -363,7 +374,7 @@ __device__ __forceinline__ TileStats softmax_tile_fast(const uint32_t tS, const 
 // Per-key path for tiles that contain masked keys: compact (rolled) code, used at most once per row
 // with valid-length padding.
 __device__ __forceinline__ TileStats softmax_tile_mixed(const uint32_t tS, const float c2s, const float row_scale,
-                                                        const float scale_qk, const uint32_t* mask_words) {
+                                                        const float scale_qk, const float p_mul, const uint32_t* mask_words) {
   uint32_t r[32];
   int max_a = INT_MIN, max_b = INT_MIN;
 #pragma unroll 1
@@ -371,7 +382,7 @@ __device__ __forceinline__ TileStats softmax_tile_mixed(const uint32_t tS, const
     tmem_ld32(tS + c * 32, r);
     chunk_max<true, 32>(r, mask_words[c], max_a, max_b);
   }
-  const RowConsts k = row_consts(max(max_a, max_b), c2s, row_scale, scale_qk);
+  const RowConsts k = row_consts(max(max_a, max_b), c2s, row_scale, scale_qk, p_mul);
   float2 sum[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll 1
   for (int c = 0; c < 4; ++c) {
@@ -427,7 +438,7 @@ __device__ __forceinline__ bool softmax_unit(const FwdParams& p, FwdCtl<FwdCfg<D
     if ((threadIdx.x >> 5 & 3) == FMHA_TRACE_Q) FMHA_STAMP(w * 4 + 0, j);
 
     TileStats st;
-    if (info->mixed[j] != 0) st = softmax_tile_mixed(tS, p.c2, p.row_scale, p.scale_qk, &info->maskbits[4 * info->live[j]]);
+    if (info->mixed[j] != 0) st = softmax_tile_mixed(tS, p.c2, p.row_scale, p.scale_qk, p.p_mul, &info->maskbits[4 * info->live[j]]);
     else st = softmax_tile_fast(tS, p, 12 + w, j);
     tmem_wait_st();
     tc_fence_before();
@@ -440,10 +451,11 @@ __device__ __forceinline__ bool softmax_unit(const FwdParams& p, FwdCtl<FwdCfg<D
     const float e_cur = clear_low2(__expf(st.m_tile - m_new));       // 22 significant bits: kMagic*e_cur is exact
     l_run = fmaf(e_old, l_run, e_cur * st.l_tile);
     m_run = m_new;
-    const float2 neg_ec = make_float2(-e_cur, -e_cur), e_bias = make_float2(e_cur * kMagic, e_cur * kMagic);
+    const float es = p.o_sign * e_cur;                               // the accumulator holds bias + o_sign * (P.V)
+    const float2 neg_ec = make_float2(es, es), e_bias = make_float2(-es * kMagic, -es * kMagic);
     const float2 e_old2 = make_float2(e_old, e_old);
 
-    // ---- drain O~ = bias - (P8 . V) into the fp32 running row
+    // ---- drain O~ = bias -/+ (P8 . V) into the fp32 running row
     ok = __all_sync(0xFFFFFFFFu, mbar_wait(bar_o, ph, abort_flag));
     if (!ok) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_O_READY, j); break; }
     tc_fence_after();
@@ -463,9 +475,9 @@ __device__ __forceinline__ bool softmax_unit(const FwdParams& p, FwdCtl<FwdCfg<D
   }
 
   // ---- epilogue (inc/fmha_i8.cuh:318-332): normalise, requantise, 16-byte stores
-  if (ok && q_row < p.S) {
+  if (ok && q_row < p.Sq) {
     const float inv = (n_live > 0 && l_run > 0.f) ? 1.0f / l_run : 0.f;
-    int8_t* dst = p.o + (static_cast<int64_t>(bh_local) * p.S + q_row) * D;
+    int8_t* dst = p.o + (static_cast<int64_t>(bh_local) * p.Sq + q_row) * D;
 #pragma unroll
     for (int c = 0; c < D / 16; ++c) {
       uint32_t wds[4];
@@ -498,7 +510,7 @@ __device__ __forceinline__ UnitGeom unit_geom(const FwdParams& p, int u) {
   const int pair = u - g.bh_local * p.q_pairs;
   g.batch = (p.bh_begin + g.bh_local) / p.H;
   g.q_row0 = pair * 2 * kTile;
-  g.nq = (g.q_row0 + kTile < p.S) ? 2 : 1;
+  g.nq = (g.q_row0 + kTile < p.Sq) ? 2 : 1;
   return g;
 }
 
@@ -649,7 +661,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // ---------------------------------------------------------------- MMA issuer
       if (lane == 0) {
         constexpr uint32_t idesc_s = make_idesc_i8(kTile, false);   // S = Q.K^T : N = 128 keys, both K-major
-        constexpr uint32_t idesc_o = make_idesc_i8(D, true);        // O = P.V   : N = D, V is MN-major
+        const uint32_t idesc_o = p.p_unsigned ? make_idesc_i8(D, true, true) : make_idesc_i8(D, true, false);   // O = P.V : N = D, V is MN-major
         constexpr uint32_t idesc_bias_s = make_idesc_f16(kTile);
         constexpr uint32_t idesc_bias_o = make_idesc_f16(D);
         const uint64_t d_bias_a = make_smem_desc_noswizzle(smem_u32(bias_a), 128, 256);

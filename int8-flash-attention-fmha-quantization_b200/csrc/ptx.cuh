@@ -223,11 +223,12 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 }
 
 // ---------------------------------------------------------------- descriptors
-// Instruction descriptor for kind::i8: int32 accumulator, signed 8-bit A and B, M = 128.
-//   bits 4-5 D format (2 = s32) | 7-9 A format (1 = s8) | 10-12 B format (1 = s8)
+// Instruction descriptor for kind::i8: int32 accumulator, 8-bit A (signed unless a_unsigned) and signed
+// 8-bit B, M = 128.
+//   bits 4-5 D format (2 = s32) | 7-9 A format (0 = u8, 1 = s8) | 10-12 B format (1 = s8)
 //   bit 15 A major (0 = K) | bit 16 B major (0 = K, 1 = MN) | 17-22 N>>3 | 24-28 M>>4
-__host__ __device__ constexpr uint32_t make_idesc_i8(int n, bool b_mn_major) {
-  return (2u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+__host__ __device__ constexpr uint32_t make_idesc_i8(int n, bool b_mn_major, bool a_unsigned = false) {
+  return (2u << 4) | ((a_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) |
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
 }
 

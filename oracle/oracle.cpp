@@ -62,10 +62,11 @@ void parallel_for(int n, int n_threads, F f) {
   for (auto& th : pool) th.join();
 }
 
-inline int8_t clamp_round_even(float x, float lo, float hi) {
+inline int32_t clamp_round_even_i32(float x, float lo, float hi) {
   x = std::fmax(std::fmin(x, hi), lo);
-  return static_cast<int8_t>(std::nearbyintf(x));  // default mode: round-half-even, like __float2int_rn
+  return static_cast<int32_t>(std::nearbyintf(x));  // default mode: round-half-even, like __float2int_rn
 }
+inline int8_t clamp_round_even(float x, float lo, float hi) { return static_cast<int8_t>(clamp_round_even_i32(x, lo, hi)); }
 
 }  // namespace
 
@@ -122,23 +123,24 @@ void oracle_qk_int32(const int8_t* q, const int8_t* k, int BH, int S, int D, int
 // Tier A.  fp32 attention on unquantised inputs with exactly the operation order of the
 // reference CPU path: S = sum_d q*k (float accumulate, d ascending), then per row
 // max(s*scale), sum of exp(s*scale - max), p = exp(..)/sum, O = sum_j p*v (j ascending).
-// mask[b, j] == 1 marks a masked key (inc/cpuSoftmax.hpp:9,24).  Rows whose keys are all
+// q and o have Sq rows per head, k and v have S (the reference CPU templates take both lengths,
+// inc/cpuSoftmax.hpp:12).  mask[b, j] == 1 marks a masked key (inc/cpuSoftmax.hpp:9,24).  Rows whose keys are all
 // masked produce 0 * (1/0)-free zeros in the reference (p is forced to 0), so O = 0.
 // p_abs_max (optional) receives max |p| (the unused s_max of test_fmha_i8.cpp:152).
-void oracle_fp32_attention(const float* q, const float* k, const float* v, const int8_t* mask,
-                           int B, int H, int S, int D, float* o, float* p_abs_max, int n_threads) {
+void oracle_fp32_attention_x(const float* q, const float* k, const float* v, const int8_t* mask,
+                             int B, int H, int Sq, int S, int D, float* o, float* p_abs_max, int n_threads) {
   const float scale = 1 / std::sqrt(static_cast<float>(D));
   std::vector<float> pmax(static_cast<size_t>(B) * H, 0.f);
   parallel_for(B * H, n_threads, [&, scale](int bh) {
     const int b = bh / H;
-    const float* qb = q + static_cast<int64_t>(bh) * S * D;
+    const float* qb = q + static_cast<int64_t>(bh) * Sq * D;
     const float* kb = k + static_cast<int64_t>(bh) * S * D;
     const float* vb = v + static_cast<int64_t>(bh) * S * D;
     const int8_t* mb = mask + static_cast<int64_t>(b) * S;
-    float* ob = o + static_cast<int64_t>(bh) * S * D;
+    float* ob = o + static_cast<int64_t>(bh) * Sq * D;
     std::vector<float> s(S), p(S);
     float local_pmax = 0.f;
-    for (int i = 0; i < S; ++i) {
+    for (int i = 0; i < Sq; ++i) {
       for (int j = 0; j < S; ++j) {
         float acc = 0;
         for (int d = 0; d < D; ++d) acc += qb[i * D + d] * kb[j * D + d];
@@ -169,22 +171,34 @@ void oracle_fp32_attention(const float* q, const float* k, const float* v, const
   }
 }
 
+// Self-attention form (the only one the reference test exercises): Sq == S.
+void oracle_fp32_attention(const float* q, const float* k, const float* v, const int8_t* mask,
+                           int B, int H, int S, int D, float* o, float* p_abs_max, int n_threads) {
+  oracle_fp32_attention_x(q, k, v, mask, B, H, S, S, D, o, p_abs_max, n_threads);
+}
+
 // Tier C ("Q128").  Quantised attention with key tiles of 128 starting at key 0 (the last tile
 // is 64 wide when S % 128 == 64), P quantised to 8 bits against each tile's own row maximum,
 // tiles merged in fp32 and the running output renormalised after every tile.
 //   amax = {q_amax, k_amax, v_amax, o_amax}
-//   rows = optional list of flattened row ids (bh * S + i); nullptr => every row.
+//   rows = optional list of flattened row ids (bh * Sq + i); nullptr => every row.
 //          Output is written at out[r * D ...] for the r-th listed row (or at the row's natural
 //          position when rows == nullptr).
 // Tiles whose keys are all masked contribute nothing and are skipped; a row with no unmasked key
 // yields zeros.
-void oracle_q128(const int8_t* q, const int8_t* k, const int8_t* v, const int8_t* mask,
-                 int B, int H, int S, int D, const float* amax,
-                 const int64_t* rows, int64_t n_rows, int8_t* out, int n_threads) {
+void oracle_q128_x(const int8_t* q, const int8_t* k, const int8_t* v, const int8_t* mask,
+                   int B, int H, int Sq, int S, int D, const float* amax, int p_levels,
+                   const int64_t* rows, int64_t n_rows, int8_t* out, int n_threads) {
+  // p_levels == 128: P8 = -rn(128 p) in [-128, 0], the reference kernel's quantisation (fmha_i8.cuh:241-250).
+  // p_levels == 255: P8 = rn(255 p) in [0, 255], the unsigned variant the reference README plans
+  //                  (README.md:137-143,186), with the final scale v_amax / (o_amax * 255).
+  const float p_mul = (p_levels == 255) ? 255.f : -128.f;
+  const float p_lo = std::min(p_mul, 0.f), p_hi = std::max(p_mul, 0.f);
+  const float o_sign = (p_levels == 255) ? 1.f : -1.f;
   const float row_scale = 1.0f / newton_sqrt(static_cast<float>(D));          // fmha_i8.cuh:71
   const float scale_qk = amax[0] * amax[1] / (127.f * 127.f);                  // fmha_i8.cuh:72
-  const float scale_v_out = amax[2] * (1.0f / (amax[3] * 128.f));              // fmha_i8.cuh:318
-  const int64_t total = rows ? n_rows : static_cast<int64_t>(B) * H * S;
+  const float scale_v_out = amax[2] * (1.0f / (amax[3] * ((p_levels == 255) ? 255.f : 128.f)));   // fmha_i8.cuh:318
+  const int64_t total = rows ? n_rows : static_cast<int64_t>(B) * H * Sq;
   const int chunks = static_cast<int>(std::min<int64_t>(total, 4096));
   parallel_for(chunks, n_threads, [=](int c) {
     std::vector<float> sf(128), o(D);
@@ -192,10 +206,10 @@ void oracle_q128(const int8_t* q, const int8_t* k, const int8_t* v, const int8_t
     int32_t p8[128];
     for (int64_t idx = c; idx < total; idx += chunks) {
       const int64_t r = rows ? rows[idx] : idx;
-      const int64_t bh = r / S;
-      const int i = static_cast<int>(r % S);
+      const int64_t bh = r / Sq;
+      const int i = static_cast<int>(r % Sq);
       const int b = static_cast<int>(bh / H);
-      const int8_t* qr = q + (bh * S + i) * D;
+      const int8_t* qr = q + (bh * Sq + i) * D;
       const int8_t* kb = k + bh * S * D;
       const int8_t* vb = v + bh * S * D;
       const int8_t* mb = mask + static_cast<int64_t>(b) * S;
@@ -218,7 +232,7 @@ void oracle_q128(const int8_t* q, const int8_t* k, const int8_t* v, const int8_t
         for (int c2 = 0; c2 < w; ++c2) {
           float p = (mb[j0 + c2] != 0) ? 0.f : expf(sf[c2] - m_t);            // fmha_i8.cuh:218-221
           l_t += p;
-          p8[c2] = static_cast<int32_t>(clamp_round_even(-128.f * p, -128.f, 0.f));  // fmha_i8.cuh:241-250 (negated)
+          p8[c2] = clamp_round_even_i32(p_mul * p, p_lo, p_hi);                      // fmha_i8.cuh:241-250 (negated when signed)
         }
         std::fill(ot.begin(), ot.end(), 0);
         for (int c2 = 0; c2 < w; ++c2) {
@@ -232,7 +246,7 @@ void oracle_q128(const int8_t* q, const int8_t* k, const int8_t* v, const int8_t
         const float l_new = e_old * l_run + e_cur * l_t;
         const float rcp = 1.0f / l_new;
         for (int d = 0; d < D; ++d)                                            // fmha_i8.cuh:309-310
-          o[d] = rcp * (l_run * e_old * o[d] + e_cur * (-1.f * static_cast<float>(ot[d])));
+          o[d] = rcp * (l_run * e_old * o[d] + e_cur * (o_sign * static_cast<float>(ot[d])));
         l_run = l_new;
         m_run = m_new;
       }
@@ -240,6 +254,13 @@ void oracle_q128(const int8_t* q, const int8_t* k, const int8_t* v, const int8_t
       for (int d = 0; d < D; ++d) dst[d] = clamp_round_even(scale_v_out * o[d], -127.f, 127.f);  // :327-328
     }
   });
+}
+
+// The reference kernel's own case: self-attention, signed P with 128 levels.
+void oracle_q128(const int8_t* q, const int8_t* k, const int8_t* v, const int8_t* mask,
+                 int B, int H, int S, int D, const float* amax,
+                 const int64_t* rows, int64_t n_rows, int8_t* out, int n_threads) {
+  oracle_q128_x(q, k, v, mask, B, H, S, S, D, amax, 128, rows, n_rows, out, n_threads);
 }
 
 // The constant the device kernel and tier C share for 1/sqrt(head_dim).

@@ -50,6 +50,10 @@ def lib():
                                             _f32p, _c.POINTER(_c.c_float), _c.c_int]
         L.oracle_q128.argtypes = [_i8p, _i8p, _i8p, _i8p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _f32p,
                                   _c.c_void_p, _c.c_int64, _i8p, _c.c_int]
+        L.oracle_fp32_attention_x.argtypes = [_f32p, _f32p, _f32p, _i8p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                              _f32p, _c.POINTER(_c.c_float), _c.c_int]
+        L.oracle_q128_x.argtypes = [_i8p, _i8p, _i8p, _i8p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _f32p,
+                                    _c.c_int, _c.c_void_p, _c.c_int64, _i8p, _c.c_int]
         L.oracle_row_scale.restype = _c.c_float
         L.oracle_row_scale.argtypes = [_c.c_int]
         _lib = L
@@ -87,21 +91,28 @@ def qk_int32(q8, k8, threads=None):
 
 
 def fp32_attention(q, k, v, mask, threads=None):
-    """Tier A.  q,k,v float32 [B,H,S,D]; mask int8 [B,S] (1 = masked key).  Returns (o, max|p|)."""
-    B, H, S, D = q.shape
-    o = np.empty((B, H, S, D), np.float32)
+    """Tier A.  q float32 [B,H,Sq,D]; k,v float32 [B,H,Sk,D] (Sq == Sk in the reference's tests);
+    mask int8 [B,Sk] (1 = masked key).  Returns (o [B,H,Sq,D], max|p|)."""
+    B, H, Sq, D = q.shape
+    Sk = k.shape[2]
+    assert k.shape == (B, H, Sk, D) and v.shape == (B, H, Sk, D) and mask.shape == (B, Sk)
+    o = np.empty((B, H, Sq, D), np.float32)
     pmax = _c.c_float(0)
-    lib().oracle_fp32_attention(np.ascontiguousarray(q, np.float32).ravel(), np.ascontiguousarray(k, np.float32).ravel(),
-                                np.ascontiguousarray(v, np.float32).ravel(), np.ascontiguousarray(mask, np.int8).ravel(),
-                                B, H, S, D, o.ravel(), _c.byref(pmax), threads or n_threads_default())
+    lib().oracle_fp32_attention_x(np.ascontiguousarray(q, np.float32).ravel(), np.ascontiguousarray(k, np.float32).ravel(),
+                                  np.ascontiguousarray(v, np.float32).ravel(), np.ascontiguousarray(mask, np.int8).ravel(),
+                                  B, H, Sq, Sk, D, o.ravel(), _c.byref(pmax), threads or n_threads_default())
     return o, float(pmax.value)
 
 
-def q128(q8, k8, v8, mask, amax4, rows=None, threads=None):
-    """Tier C.  int8 [B,H,S,D] inputs, mask int8 [B,S] (non-zero = masked key),
-    amax4 = (q_amax, k_amax, v_amax, o_amax).  rows: optional int64 array of flattened row ids
-    (bh*S + i); returns int8 [len(rows), D] then, else int8 [B,H,S,D]."""
-    B, H, S, D = q8.shape
+def q128(q8, k8, v8, mask, amax4, rows=None, threads=None, p_levels=128):
+    """Tier C.  q8 int8 [B,H,Sq,D]; k8,v8 int8 [B,H,Sk,D]; mask int8 [B,Sk] (non-zero = masked key),
+    amax4 = (q_amax, k_amax, v_amax, o_amax).  p_levels 128 = the reference kernel's signed P, 255 = the
+    unsigned variant.  rows: optional int64 array of flattened row ids (bh*Sq + i); returns int8
+    [len(rows), D] then, else int8 [B,H,Sq,D]."""
+    B, H, Sq, D = q8.shape
+    Sk = k8.shape[2]
+    assert k8.shape == (B, H, Sk, D) and v8.shape == (B, H, Sk, D) and mask.shape == (B, Sk)
+    assert p_levels in (128, 255)
     a = np.asarray(amax4, np.float32)
     assert a.size == 4
     q8 = np.ascontiguousarray(q8, np.int8)
@@ -109,14 +120,14 @@ def q128(q8, k8, v8, mask, amax4, rows=None, threads=None):
     v8 = np.ascontiguousarray(v8, np.int8)
     mask = np.ascontiguousarray(mask, np.int8)
     if rows is None:
-        out = np.empty((B, H, S, D), np.int8)
-        lib().oracle_q128(q8.ravel(), k8.ravel(), v8.ravel(), mask.ravel(), B, H, S, D, a, None, 0, out.ravel(),
-                          threads or n_threads_default())
+        out = np.empty((B, H, Sq, D), np.int8)
+        lib().oracle_q128_x(q8.ravel(), k8.ravel(), v8.ravel(), mask.ravel(), B, H, Sq, Sk, D, a, p_levels, None, 0,
+                            out.ravel(), threads or n_threads_default())
     else:
         rows = np.ascontiguousarray(rows, np.int64)
         out = np.empty((rows.size, D), np.int8)
-        lib().oracle_q128(q8.ravel(), k8.ravel(), v8.ravel(), mask.ravel(), B, H, S, D, a,
-                          rows.ctypes.data_as(_c.c_void_p), rows.size, out.ravel(), threads or n_threads_default())
+        lib().oracle_q128_x(q8.ravel(), k8.ravel(), v8.ravel(), mask.ravel(), B, H, Sq, Sk, D, a, p_levels,
+                            rows.ctypes.data_as(_c.c_void_p), rows.size, out.ravel(), threads or n_threads_default())
     return out
 
 
@@ -152,6 +163,9 @@ def ref_cpu(native=False):
                                                   _c.c_int, _c.c_int, _f32p, _c.c_int]
         L.ref_mean_rel_deviation.restype = _c.c_double
         L.ref_mean_rel_deviation.argtypes = [_i8p, _f32p, _c.c_int, _c.c_float]
+        L.ref_fp32_attention_cross.argtypes = [_f32p, _f32p, _f32p, _i32p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                               _f32p, _f32p, _f32p]
+        L.ref_qk_int32_cross.argtypes = [_i8p, _i8p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _i32p]
         _ref[key] = L
     return _ref[key]
 
@@ -173,6 +187,20 @@ def ref_fp32_attention(q, k, v, mask, batched=True, threads=None, native=False):
         return o.reshape(B, H, S, D), float(smax.value)
     L.ref_fp32_attention_threaded(q, k, v, m, H, S, D, 0, B * H, o, threads or n_threads_default())
     return o.reshape(B, H, S, D), None
+
+
+def ref_fp32_attention_cross(q, k, v, mask):
+    """The reference CPU templates called with Sq != Sk: q [B,H,Sq,D], k,v [B,H,Sk,D], mask [B,Sk]."""
+    B, H, Sq, D = q.shape
+    Sk = k.shape[2]
+    L = ref_cpu(False)
+    o = np.zeros(B * H * Sq * D, np.float32)
+    s = np.zeros(B * H * Sq * Sk, np.float32)
+    p = np.zeros(B * H * Sq * Sk, np.float32)
+    L.ref_fp32_attention_cross(np.ascontiguousarray(q, np.float32).ravel(), np.ascontiguousarray(k, np.float32).ravel(),
+                               np.ascontiguousarray(v, np.float32).ravel(), np.ascontiguousarray(mask).astype(np.int32).ravel(),
+                               B, H, Sq, Sk, D, s, p, o)
+    return o.reshape(B, H, Sq, D)
 
 
 def ref_gpu():

@@ -67,6 +67,29 @@ void ref_fp32_attention_batched(float* q, float* k, float* v, int* mask_i32, int
                                       GEMM_OP_T, GEMM_OP_T, nullptr, false);
 }
 
+// The same three calls with a different number of query rows (Sq) and keys (Sk): the reference templates
+// take both lengths (inc/cpuGEMM.hpp:10-13 M,N,K; inc/cpuSoftmax.hpp:12 seq_len_q, seq_len_k) although
+// its test only ever passes Sq == Sk.  q,o: [B,H,Sq,D]; k,v: [B,H,Sk,D]; mask [B,Sk]; s_buf/p_buf hold
+// B*H*Sq*Sk floats.
+void ref_fp32_attention_cross(float* q, float* k, float* v, int* mask_i32, int B, int H, int Sq, int Sk,
+                              int D, float* s_buf, float* p_buf, float* o) {
+  const int64_t len_sp = static_cast<int64_t>(B) * H * Sq * Sk;
+  std::memset(s_buf, 0, sizeof(float) * len_sp);
+  std::memset(p_buf, 0, sizeof(float) * len_sp);
+  std::memset(o, 0, sizeof(float) * static_cast<int64_t>(B) * H * Sq * D);
+  cpuGEMM<float, float, float, float>(q, k, s_buf, Sq, Sk, D, Sq * D, Sk * D, Sq * Sk, B * H, 1.f, 0.f,
+                                      GEMM_OP_T, GEMM_OP_N, nullptr, false);
+  cpuAttentionMaskedSoftmax<float, float>(s_buf, p_buf, mask_i32, B, Sq, Sk, H, D);
+  cpuGEMM<float, float, float, float>(p_buf, v, o, Sq, D, Sk, Sq * Sk, Sk * D, Sq * D, B * H, 1.f, 0.f,
+                                      GEMM_OP_T, GEMM_OP_T, nullptr, false);
+}
+
+// Exact int32 Q.K^T for Sq query rows against Sk keys.
+void ref_qk_int32_cross(int8_t* q, int8_t* k, int BH, int Sq, int Sk, int D, int32_t* s) {
+  cpuGEMM<int32_t, int32_t, int8_t, int32_t>(q, k, s, Sq, Sk, D, Sq * D, Sk * D, Sq * Sk, BH, 1, 0,
+                                             GEMM_OP_T, GEMM_OP_N, nullptr, false);
+}
+
 // Same arithmetic, one unchanged single-slice call chain per (b,h), slices spread over threads.
 // This is the timed CPU baseline; nbh may be a subset of B*H (heads [bh0, bh0+nbh)).
 void ref_fp32_attention_threaded(float* q, float* k, float* v, int* mask_i32, int H, int S, int D,

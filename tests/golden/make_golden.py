@@ -10,10 +10,13 @@ reference code:
                   called as in test_fmha_i8.cpp:142-159;  ref_s_max = abs_max(P) (:152)
     ref_dev_pct   compareResultsWithGoldenI8 (inc/utils.hpp:59-89) applied to the int8 array
                   `probe_o8` against ref_o_fp32
+The file cross_b1h2q96k192d64.npz holds the same reference outputs for a problem with 96 query rows
+against 192 keys (the reference CPU templates take both lengths; its test never uses that).
 `oracle_o8` is NOT a reference output: it is the tier-C restatement's result at generation time,
 kept to notice drift of the restatement.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py            # every fixture
+    python tests/golden/make_golden.py cross      # only the Sq != Sk fixture
 """
 import os
 import sys
@@ -61,6 +64,9 @@ def main():
     mask[:, 128:256] = 1
     cases["hole_b1h1s320d64"] = (q, k, v, mask)
 
+    make_cross(oracle, R)
+    if "cross" in sys.argv[1:]:
+        return
     for name, (q, k, v, mask) in cases.items():
         B, H, S, D = q.shape
         qa = float(R.ref_abs_max(q.ravel(), q.size))
@@ -83,6 +89,33 @@ def main():
                             oracle_o8=o8)
         print(f"{name}: B{B} H{H} S{S} D{D} amax=({qa:.4f},{ka:.4f},{va:.4f},{oa:.4f}) s_max={s_max:.4f} "
               f"ref_dev={dev:.4f}% -> {os.path.getsize(path)} bytes")
+
+
+def make_cross(oracle, R):
+    """96 query rows against 192 keys, the reference test's value distributions, random 20 % key mask."""
+    B, H, Sq, Sk, D = 1, 2, 96, 192, 64
+    rng = np.random.Generator(np.random.Philox(key=424242))
+    mask = (rng.random((B, Sk)) < 0.2).astype(np.int8)
+    q = (rng.random((B, H, Sq, D), dtype=np.float32) - np.float32(0.5)).astype(np.float32)
+    k = (rng.random((B, H, Sk, D), dtype=np.float32) - np.float32(0.5)).astype(np.float32)
+    v = np.abs(rng.random((B, H, Sk, D), dtype=np.float32) - np.float32(0.5)).astype(np.float32)
+    qa = float(R.ref_abs_max(q.ravel(), q.size))
+    ka = float(R.ref_abs_max(k.ravel(), k.size))
+    va = float(R.ref_abs_max(v.ravel(), v.size))
+    q8 = np.empty(q.shape, np.int8); R.ref_quantize(q.ravel(), q.size, qa, q8.ravel())
+    k8 = np.empty(k.shape, np.int8); R.ref_quantize(k.ravel(), k.size, ka, k8.ravel())
+    v8 = np.empty(v.shape, np.int8); R.ref_quantize(v.ravel(), v.size, va, v8.ravel())
+    s32 = np.empty((B, H, Sq, Sk), np.int32)
+    R.ref_qk_int32_cross(q8.ravel(), k8.ravel(), B * H, Sq, Sk, D, s32.ravel())
+    o = oracle.ref_fp32_attention_cross(q, k, v, mask)
+    oa = float(R.ref_abs_max(o.ravel(), o.size))
+    o8 = oracle.q128(q8, k8, v8, mask, (qa, ka, va, oa))
+    o8u = oracle.q128(q8, k8, v8, mask, (qa, ka, va, oa), p_levels=255)
+    path = os.path.join(HERE, "cross_b1h2q96k192d64.npz")
+    np.savez_compressed(path, q=q, k=k, v=v, mask=mask, ref_q8=q8, ref_k8=k8, ref_v8=v8,
+                        ref_amax=np.array([qa, ka, va, oa], np.float32), ref_s_int32=s32, ref_o_fp32=o,
+                        oracle_o8=o8, oracle_o8_uint8p=o8u)
+    print(f"cross: B{B} H{H} Sq{Sq} Sk{Sk} D{D} amax=({qa:.4f},{ka:.4f},{va:.4f},{oa:.4f}) -> {os.path.getsize(path)} bytes")
 
 
 if __name__ == "__main__":

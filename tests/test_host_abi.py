@@ -68,6 +68,18 @@ def test_host_side_rejections(pkg):
     assert L.fmha_i8_sm100_infer_slice(None, a, d, *vp, 1, 2, 1) == pkg.ERR_BAD_SLICE
     assert L.fmha_i8_sm100_infer_slice(None, a, d, *vp, -1, 1, 1) == pkg.ERR_BAD_SLICE
     assert "seq_len" in pkg.status_string(pkg.ERR_BAD_SHAPE)
+    # flags: bit 1 (unsigned P) is defined, anything above is not
+    assert _call(pkg, good, flags=1 | 4) == pkg.ERR_BAD_FLAGS
+    assert _call(pkg, good, flags=2) == pkg.ERR_NO_CUDA_CORE_PATH
+    # query rows != keys: desc5 = {batch, seq_q, seq_k, head, dim}; seq_q free, seq_k a multiple of 64
+    def cross(desc5, begin=0, count=2):
+        return L.fmha_i8_sm100_infer_cross(None, a, (ctypes.c_int * 5)(*desc5), *vp, begin, count, 1)
+    assert cross((1, 0, 128, 2, 64)) == pkg.ERR_BAD_SHAPE
+    assert cross((1, 40000, 128, 2, 64)) == pkg.ERR_BAD_SHAPE
+    assert cross((1, 7, 100, 2, 64)) == pkg.ERR_BAD_SHAPE
+    assert cross((1, 7, 128, 2, 32)) == pkg.ERR_BAD_SHAPE
+    assert cross((1, 7, 128, 2, 64), begin=1, count=2) == pkg.ERR_BAD_SLICE
+    assert L.fmha_i8_sm100_infer_cross(None, a, None, *vp, 0, 2, 1) == pkg.ERR_NULL_POINTER
     assert pkg.lib().fmha_i8_sm100_version() >= 100
 
 

@@ -5,7 +5,10 @@ import os
 import numpy as np
 import pytest
 
-GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+# self-attention fixtures; the cross_* file (query rows != keys) has its own tests
+GOLDEN = sorted(p for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz"))
+                if not os.path.basename(p).startswith("cross_"))
+GOLDEN_CROSS = os.path.join(os.path.dirname(__file__), "golden", "cross_b1h2q96k192d64.npz")
 
 
 def test_golden_files_present():
@@ -91,3 +94,47 @@ def test_fp32_golden_matches_reference_live(oracle):
     assert np.array_equal(o_ref, o_thr)
     assert np.array_equal(o_ref, o)
     assert np.float32(pmax) == np.float32(s_max)
+
+
+# ---- query rows != keys (the reference CPU templates take both lengths) and the unsigned-P variant
+
+@pytest.fixture(scope="module")
+def cross():
+    return dict(np.load(GOLDEN_CROSS))
+
+
+def test_cross_fp32_golden_bit_exact(cross, oracle):
+    o, _ = oracle.fp32_attention(cross["q"], cross["k"], cross["v"], cross["mask"])
+    assert o.shape == cross["ref_o_fp32"].shape == (1, 2, 96, 64)
+    assert np.array_equal(o, cross["ref_o_fp32"])
+    assert np.float32(np.abs(o).max()) == cross["ref_amax"][3]
+
+
+def test_cross_qk_int32_matches_reference_gemm(cross):
+    s = np.einsum("bhid,bhjd->bhij", cross["ref_q8"].astype(np.int32), cross["ref_k8"].astype(np.int32))
+    assert np.array_equal(s, cross["ref_s_int32"])
+
+
+@pytest.mark.parametrize("p_levels,key", [(128, "oracle_o8"), (255, "oracle_o8_uint8p")])
+def test_cross_q128_meets_reference_criterion_and_stays_put(cross, oracle, p_levels, key):
+    amax = tuple(float(x) for x in cross["ref_amax"])
+    o8 = oracle.q128(cross["ref_q8"], cross["ref_k8"], cross["ref_v8"], cross["mask"], amax, p_levels=p_levels)
+    assert oracle.mean_rel_deviation(o8, cross["ref_o_fp32"], amax[3]) < 20.0
+    assert np.array_equal(o8, cross[key])
+    rows = np.array([0, 95, 96, 191, 100], np.int64)          # flattened bh*Sq + i
+    sub = oracle.q128(cross["ref_q8"], cross["ref_k8"], cross["ref_v8"], cross["mask"], amax, rows=rows, p_levels=p_levels)
+    assert np.array_equal(sub, o8.reshape(-1, 64)[rows])
+
+
+def test_unsigned_p_is_closer_to_fp32_than_signed_p(oracle):
+    """255 levels instead of 128 for the probabilities: the quantisation error of P halves, so the int8
+    output sits closer to the fp32 golden (what the reference README expects of its planned variant)."""
+    errs = {}
+    for path in GOLDEN:
+        case = dict(np.load(path))
+        amax = tuple(float(x) for x in case["ref_amax"])
+        ideal = case["ref_o_fp32"] * (127.0 / amax[3])
+        for lv in (128, 255):
+            o8 = oracle.q128(case["ref_q8"], case["ref_k8"], case["ref_v8"], case["mask"], amax, p_levels=lv)
+            errs.setdefault(lv, []).append(float(np.mean((o8.astype(np.float64) - ideal) ** 2)))
+    assert sum(errs[255]) < sum(errs[128])
