@@ -87,6 +87,16 @@ int fmha_i8_sm100_infer_cross(void* stream, const float amax[5], const int desc5
                               const void* q, const void* k, const void* v, const void* mask, void* o,
                               int bh_begin, int bh_count, unsigned flags);
 
+/* Calibration of o_amax on the device.  The reference takes o_amax = max|O| from its fp32 CPU attention
+ * (test_fmha_i8.cpp:161) before it can call the int8 kernel at all; this runs the same int8 pipeline
+ * (same kernel, same tiles) but instead of storing O8 it writes the largest magnitude of the unquantised
+ * output, in real units, to the device float *o_amax_out (zeroed first, on the same stream).  amax[0..2]
+ * = q, k, v ranges; amax[3], amax[4] are ignored.  desc5 and flags as in fmha_i8_sm100_infer_cross; o is
+ * not needed.  Feeding the result back as o_amax makes the largest output element quantise to +-127. */
+int fmha_i8_sm100_calibrate_o_amax(void* stream, const float amax[5], const int desc5[5],
+                                   const void* q, const void* k, const void* v, const void* mask,
+                                   float* o_amax_out, unsigned flags);
+
 /* End-to-end form of the caller in test_fmha_i8.cpp:165-178,204,236: HOST buffers in, HOST
  * buffer out.  Copies q,k,v,mask to device staging buffers owned by the library (grown on demand,
  * kept for reuse), runs the forward pass, copies o back and synchronises.  The work is pipelined

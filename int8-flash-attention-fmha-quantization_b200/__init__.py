@@ -31,7 +31,7 @@ FLAG_USE_TCU = 1
 FLAG_UINT8_P = 2     # P quantised as unsigned 8 bit, 255 levels (the reference README's planned variant)
 
 EXPORTS = (
-    "fmha_i8_sm100_infer", "fmha_i8_sm100_infer_slice", "fmha_i8_sm100_infer_cross", "fmha_i8_sm100_infer_host",
+    "fmha_i8_sm100_infer", "fmha_i8_sm100_infer_slice", "fmha_i8_sm100_infer_cross", "fmha_i8_sm100_calibrate_o_amax", "fmha_i8_sm100_infer_host",
     "fmha_i8_sm100_debug_qk", "fmha_i8_sm100_debug_pv", "fmha_i8_sm100_debug_simt", "fmha_i8_sm100_debug_simt_x",
     "fmha_i8_sm100_quantize_f32", "fmha_i8_sm100_quantize_f32_noalloc", "fmha_i8_sm100_device_status", "fmha_i8_sm100_last_status", "fmha_i8_sm100_status_string",
     "fmha_i8_sm100_launch_count", "fmha_i8_sm100_version",
@@ -97,6 +97,7 @@ def lib():
         L.fmha_i8_sm100_infer.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, u]
         L.fmha_i8_sm100_infer_slice.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, u]
         L.fmha_i8_sm100_infer_cross.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, u]
+        L.fmha_i8_sm100_calibrate_o_amax.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, u]
         L.fmha_i8_sm100_infer_host.argtypes = [fp, ip, vp, vp, vp, vp, vp, u]
         L.fmha_i8_sm100_debug_qk.argtypes = [vp, ip, vp, vp, vp]
         L.fmha_i8_sm100_debug_pv.argtypes = [vp, ip, vp, vp, vp, u]
@@ -170,6 +171,16 @@ def FMHAInferI8Cross(stream, fmha_param, attn_desc_x, q, k, v, padding_mask, o, 
     if check and st != OK:
         raise FmhaError(st, "FMHAInferI8Cross")
     return st
+
+
+def calibrate_o_amax(stream, fmha_param, attn_desc_x, q, k, v, padding_mask, o_amax_out, uint8_p=False):
+    """Largest |output| of the int8 pipeline in real units, written to the one-element float32 device tensor
+    `o_amax_out` (the reference takes this number from its fp32 CPU attention, test_fmha_i8.cpp:161).
+    Only q_amax, k_amax, v_amax of `fmha_param` are used.  Enqueues on `stream`, no synchronisation."""
+    st = lib().fmha_i8_sm100_calibrate_o_amax(_stream_handle(stream), fmha_param.as_c(), attn_desc_x.as_c(), _ptr(q), _ptr(k),
+                                              _ptr(v), _ptr(padding_mask), _ptr(o_amax_out), _flags(True, uint8_p))
+    if st != OK:
+        raise FmhaError(st, "calibrate_o_amax")
 
 
 def FMHAInferI8Slice(stream, fmha_param, attn_desc, q, k, v, padding_mask, o, bh_begin, bh_count, check=True, uint8_p=False):

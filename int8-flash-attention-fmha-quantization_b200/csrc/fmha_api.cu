@@ -176,6 +176,8 @@ int fill_params(FwdParams* p, const float amax[5], int D, unsigned flags = 0u) {
   p->p_mul = up ? 255.f : -128.f;
   p->o_sign = up ? 1.f : -1.f;
   p->p_unsigned = up ? 1u : 0u;
+  p->amax_out = nullptr;
+  p->amax_scale = amax[2] / ((up ? 255.f : 128.f) * 127.f);   // O~/l counts P in 1/128 (1/255) and V in v_amax/127
   p->c2 = static_cast<float>(static_cast<double>(p->row_scale) * static_cast<double>(p->scale_qk) * 1.4426950408889634);
   if (!(p->c2 > 0.f) || !std::isfinite(p->c2 * kMagic)) return FMHA_I8_ERR_BAD_AMAX;
   return FMHA_I8_OK;
@@ -195,19 +197,22 @@ int launch_fwd(cudaStream_t stream, DeviceInfo* dev, FwdParams p, const void* q,
   return cudaGetLastError() == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH;
 }
 
+// calib == nullptr: the forward pass into o.  calib != nullptr: calibration, o is not touched (may be null).
 int infer_x_impl(void* stream, const float amax[5], const Shape& sh, const void* q, const void* k,
-                 const void* v, const void* mask, void* o, int bh_begin, int bh_count, unsigned flags) {
-  if (!amax || !q || !k || !v || !mask || !o) return FMHA_I8_ERR_NULL_POINTER;
+                 const void* v, const void* mask, void* o, int bh_begin, int bh_count, unsigned flags,
+                 float* calib = nullptr) {
+  if (!amax || !q || !k || !v || !mask || (!o && !calib)) return FMHA_I8_ERR_NULL_POINTER;
   if (!(flags & FMHA_I8_FLAG_USE_TCU)) return FMHA_I8_ERR_NO_CUDA_CORE_PATH;
   if (flags & ~(FMHA_I8_FLAG_USE_TCU | FMHA_I8_FLAG_UINT8_P)) return FMHA_I8_ERR_BAD_FLAGS;
   int st = check_shape_x(sh);
   if (st != FMHA_I8_OK) return st;
   const long long BH = static_cast<long long>(sh.B) * sh.H;
   if (bh_begin < 0 || bh_count < 1 || static_cast<long long>(bh_begin) + bh_count > BH) return FMHA_I8_ERR_BAD_SLICE;
-  if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(o, 16) || !aligned(mask, 4))
+  if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(o, 16) || !aligned(mask, 4) || !aligned(calib, 4))
     return FMHA_I8_ERR_MISALIGNED;
   FwdParams p{};
   if ((st = fill_params(&p, amax, sh.D, flags)) != FMHA_I8_OK) return st;
+  p.amax_out = calib;
   int err = FMHA_I8_OK;
   DeviceInfo* dev = current_device(&err);
   if (!dev) return err;
@@ -303,6 +308,21 @@ int fmha_i8_sm100_infer_cross(void* stream, const float amax[5], const int desc5
   if (!desc5) return finish(FMHA_I8_ERR_NULL_POINTER);
   const Shape sh{desc5[0], desc5[1], desc5[2], desc5[3], desc5[4]};
   return finish(infer_x_impl(stream, amax, sh, q, k, v, mask, o, bh_begin, bh_count, flags));
+}
+
+int fmha_i8_sm100_calibrate_o_amax(void* stream, const float amax[5], const int desc5[5], const void* q, const void* k,
+                                   const void* v, const void* mask, float* o_amax_out, unsigned flags) {
+  if (!desc5 || !amax || !o_amax_out) return finish(FMHA_I8_ERR_NULL_POINTER);
+  const Shape sh{desc5[0], desc5[1], desc5[2], desc5[3], desc5[4]};
+  const long long BH = static_cast<long long>(sh.B) * sh.H;
+  if (BH < 1 || BH > 0x7FFFFFFFLL) return finish(FMHA_I8_ERR_BAD_SHAPE);
+  // o_amax is what is being determined: any positive placeholder passes the argument check
+  const float a[5] = {amax[0], amax[1], amax[2], 1.0f, 1.0f};
+  if (cudaMemsetAsync(o_amax_out, 0, sizeof(float), static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+    cudaGetLastError();
+    return finish(FMHA_I8_ERR_LAUNCH);
+  }
+  return finish(infer_x_impl(stream, a, sh, q, k, v, mask, nullptr, 0, static_cast<int>(BH), flags, o_amax_out));
 }
 
 int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void* host_q, const void* host_k,

@@ -100,6 +100,9 @@ struct FwdParams {
                         // +255: P8 = rn(255 p) unsigned (the reference README's planned UINT8 x INT8 variant)
   float o_sign;         // -1 when the accumulator holds -(P.V) (signed P), +1 when it holds +(P.V)
   unsigned p_unsigned;  // 1 = the tensor core reads P as unsigned bytes
+  float* amax_out;      // calibration mode when not null: nothing is stored to o; instead the largest |output|
+                        // in real units, max |O~ / l| * amax_scale, is folded into this device float
+  float amax_scale;     // v_amax / (127 * 128)  (127 * 255 with unsigned P)
   unsigned* status;     // eight device status words
 };
 
@@ -472,6 +475,21 @@ __device__ __forceinline__ bool softmax_unit(const FwdParams& p, FwdCtl<FwdCfg<D
     tc_fence_before();
     mbar_arrive(bar_f);
     if ((threadIdx.x >> 5 & 3) == FMHA_TRACE_Q) FMHA_STAMP(w * 4 + 3, j);
+  }
+
+  // ---- calibration mode: only the largest magnitude of the unquantised output is wanted (the reference
+  //      takes o_amax from its fp32 CPU result, test_fmha_i8.cpp:161)
+  if (p.amax_out != nullptr) {
+    float mx = 0.f;
+    if (ok && q_row < p.Sq && n_live > 0 && l_run > 0.f) {
+      const float inv = 1.0f / l_run;
+#pragma unroll
+      for (int i = 0; i < D / 2; ++i) mx = fmaxf(mx, fmaxf(fabsf(o2[i].x * inv), fabsf(o2[i].y * inv)));
+    }
+    // non-negative floats order like their bit patterns
+    const unsigned bits = __reduce_max_sync(0xFFFFFFFFu, __float_as_uint(mx * p.amax_scale));
+    if ((threadIdx.x & 31) == 0 && bits != 0u) atomicMax(reinterpret_cast<unsigned*>(p.amax_out), bits);
+    return ok;
   }
 
   // ---- epilogue (inc/fmha_i8.cuh:318-332): normalise, requantise, 16-byte stores

@@ -170,3 +170,35 @@ def test_cross_decode_shape_full_size(pkg, wl, oracle, torch_dev):
     want = oracle.q128(q8, k8, v8, m, amax)
     got = _run_cross(pkg, torch_dev, q8, k8, v8, m, amax)
     assert_parity(got, want, "decode shape")
+
+
+# ---------------------------------------------------------------- o_amax calibration on the device
+
+@pytest.mark.parametrize("B,H,Sq,Sk,D,up", [(2, 2, 320, 320, 64, False), (1, 3, 100, 512, 128, True), (2, 1, 1024, 1024, 128, False)])
+def test_calibrate_o_amax(pkg, wl, oracle, torch_dev, B, H, Sq, Sk, D, up):
+    """The calibrated range is the largest |output| of the int8 pipeline: close to the fp32 golden's (the
+    inputs are quantised, so not equal), and fed back it makes the largest element quantise to +-127."""
+    torch = torch_dev
+    q8, k8, v8, m, amax, o = _random_case(wl, oracle, B, H, Sq, Sk, D, seed=B * 1000 + Sq, mask_p=0.2)
+    tq, tk, tv, tm = (torch.from_numpy(x).cuda() for x in (q8, k8, v8, m))
+    out = torch.full((1,), -1.0, dtype=torch.float32, device="cuda")
+    desc = pkg.AttnDataDescriptorX(B, Sq, Sk, H, D)
+    pkg.calibrate_o_amax(None, pkg.FMHAParamI8(amax[0], amax[1], amax[2], 0.0, 0.0), desc, tq, tk, tv, tm, out, uint8_p=up)
+    _clean(pkg)
+    oa = float(out.item())
+    assert abs(oa - amax[3]) <= 0.03 * amax[3], (oa, amax[3])
+    amax2 = [amax[0], amax[1], amax[2], oa]
+    got = _run_cross(pkg, torch, q8, k8, v8, m, amax2, uint8_p=up)
+    assert int(np.abs(got.astype(np.int32)).max()) in (126, 127)
+    assert_parity(got, oracle.q128(q8, k8, v8, m, amax2, p_levels=255 if up else 128), "forward with the calibrated o_amax")
+
+
+def test_calibrate_o_amax_all_masked_is_zero(pkg, wl, oracle, torch_dev):
+    torch = torch_dev
+    q8, k8, v8, m, amax, _ = _random_case(wl, oracle, 1, 2, 64, 128, 64, seed=3)
+    m[:] = 1
+    tq, tk, tv, tm = (torch.from_numpy(x).cuda() for x in (q8, k8, v8, m))
+    out = torch.full((1,), -1.0, dtype=torch.float32, device="cuda")
+    pkg.calibrate_o_amax(None, pkg.FMHAParamI8(1.0, 1.0, 1.0, 0.0, 0.0), pkg.AttnDataDescriptorX(1, 64, 128, 2, 64), tq, tk, tv, tm, out)
+    _clean(pkg)
+    assert float(out.item()) == 0.0

@@ -80,6 +80,7 @@ def test_host_side_rejections(pkg):
     assert cross((1, 7, 128, 2, 32)) == pkg.ERR_BAD_SHAPE
     assert cross((1, 7, 128, 2, 64), begin=1, count=2) == pkg.ERR_BAD_SLICE
     assert L.fmha_i8_sm100_infer_cross(None, a, None, *vp, 0, 2, 1) == pkg.ERR_NULL_POINTER
+    assert L.fmha_i8_sm100_calibrate_o_amax(None, a, (ctypes.c_int * 5)(1, 7, 128, 2, 64), *vp[:4], None, 1) == pkg.ERR_NULL_POINTER
     assert pkg.lib().fmha_i8_sm100_version() >= 100
 
 
