@@ -129,6 +129,14 @@ int fmha_i8_sm100_debug_simt_x(void* stream, const float amax[5], const int desc
                                const void* q, const void* k, const void* v, const void* mask, void* o,
                                unsigned flags);
 
+/* Debug: shows what a host sees when a device-side wait gives up, without faulting anything.  One warp
+ * waits for at most limit_cycles (1000 ... 2e9 SM cycles) on a barrier that never completes, records
+ * FMHA_I8_DEV_WAIT_DEBUG in the status words and returns normally; the context stays usable.  While the
+ * status words are non-zero the forward kernel refuses to start (its CTAs return at once, o is not
+ * written); fmha_i8_sm100_device_status() reports and clears them.  No counterpart in the reference,
+ * which checks nothing. */
+int fmha_i8_sm100_debug_wait_probe(void* stream, long long limit_cycles);
+
 /* Per-tensor symmetric quantisation on the device, the producer step in front of the attention call:
  * amax = max|x| (abs_max, inc/utils.hpp:31-39) and q[i] = clamp(floor(x[i]*127/amax + 0.5), -127, 127)
  * (float_quant2_int8, inc/utils.hpp:23-29; the reference does both on the host, test_fmha_i8.cpp:95-110).

@@ -32,7 +32,7 @@ FLAG_UINT8_P = 2     # P quantised as unsigned 8 bit, 255 levels (the reference 
 
 EXPORTS = (
     "fmha_i8_sm100_infer", "fmha_i8_sm100_infer_slice", "fmha_i8_sm100_infer_cross", "fmha_i8_sm100_calibrate_o_amax", "fmha_i8_sm100_infer_host",
-    "fmha_i8_sm100_debug_qk", "fmha_i8_sm100_debug_pv", "fmha_i8_sm100_debug_simt", "fmha_i8_sm100_debug_simt_x",
+    "fmha_i8_sm100_debug_qk", "fmha_i8_sm100_debug_pv", "fmha_i8_sm100_debug_simt", "fmha_i8_sm100_debug_simt_x", "fmha_i8_sm100_debug_wait_probe",
     "fmha_i8_sm100_quantize_f32", "fmha_i8_sm100_quantize_f32_noalloc", "fmha_i8_sm100_device_status", "fmha_i8_sm100_last_status", "fmha_i8_sm100_status_string",
     "fmha_i8_sm100_launch_count", "fmha_i8_sm100_version",
 )
@@ -103,6 +103,7 @@ def lib():
         L.fmha_i8_sm100_debug_pv.argtypes = [vp, ip, vp, vp, vp, u]
         L.fmha_i8_sm100_debug_simt.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp]
         L.fmha_i8_sm100_debug_simt_x.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, u]
+        L.fmha_i8_sm100_debug_wait_probe.argtypes = [vp, ctypes.c_longlong]
         L.fmha_i8_sm100_quantize_f32.argtypes = [vp, vp, ctypes.c_longlong, vp, vp]
         L.fmha_i8_sm100_quantize_f32_noalloc.argtypes = [vp, vp, ctypes.c_longlong, vp, vp]
         L.fmha_i8_sm100_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
@@ -225,6 +226,13 @@ def debug_simt_x(stream, fmha_param, attn_desc_x, q, k, v, padding_mask, o, uint
                                           _ptr(v), _ptr(padding_mask), _ptr(o), FLAG_UINT8_P if uint8_p else 0)
     if st != OK:
         raise FmhaError(st, "debug_simt_x")
+
+
+def debug_wait_probe(stream, limit_cycles):
+    """Launches the one-warp kernel whose bounded wait runs out on purpose (no fault; see the C header)."""
+    st = lib().fmha_i8_sm100_debug_wait_probe(_stream_handle(stream), int(limit_cycles))
+    if st != OK:
+        raise FmhaError(st, "debug_wait_probe")
 
 
 def quantize_f32(stream, x, out, amax_out=None, n=None, entry="fmha_i8_sm100_quantize_f32"):

@@ -487,6 +487,16 @@ int fmha_i8_sm100_debug_simt(void* stream, const float amax[5], const int desc[4
   return fmha_i8_sm100_debug_simt_x(stream, amax, desc5, q, k, v, mask, o, 0u);
 }
 
+int fmha_i8_sm100_debug_wait_probe(void* stream, long long limit_cycles) {
+  if (limit_cycles < 1000 || limit_cycles > kWaitLimitCycles) return finish(FMHA_I8_ERR_TOO_LARGE);
+  int err = FMHA_I8_OK;
+  DeviceInfo* dev = current_device(&err);
+  if (!dev) return finish(err);
+  wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(dev->status, limit_cycles);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return finish(cudaGetLastError() == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH);
+}
+
 int fmha_i8_sm100_quantize_f32(void* stream, const float* x, long long n, int8_t* out, float* amax_out) {
   int st = check_quant_args(x, n, out);
   if (st != FMHA_I8_OK) return finish(st);

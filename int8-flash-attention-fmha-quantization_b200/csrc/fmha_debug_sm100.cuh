@@ -190,6 +190,23 @@ debug_pv_kernel(const __grid_constant__ CUtensorMap map_v, const int8_t* p8, int
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
 }
 
+// Exercises the give-up path of the bounded waits without any fault: one warp waits, for at most
+// `limit_cycles`, on a barrier that nothing will ever arrive on, records FMHA_I8_DEV_WAIT_DEBUG in the
+// status words when the limit is reached and returns normally.  What a host sees afterwards is exactly
+// what it would see if a wait of the forward kernel had run out.
+__global__ void __launch_bounds__(32) wait_probe_kernel(unsigned* status, long long limit_cycles) {
+  __shared__ uint64_t never;
+  __shared__ int abort_word;
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    mbar_init(smem_u32(&never), 1);
+    mbar_init_fence();
+  }
+  __syncwarp();
+  const bool done = __all_sync(0xFFFFFFFFu, mbar_wait_limited(smem_u32(&never), 0u, &abort_word, limit_cycles));
+  if (!done && threadIdx.x == 0) raise_status(&abort_word, status, FMHA_I8_DEV_WAIT_DEBUG, 4);
+}
+
 // The whole forward pass on CUDA cores, one thread per query row, in the operation order of the
 // reference kernel's arithmetic (inc/fmha_i8.cuh:183-253,298-332): expf, per-tile renormalised
 // running output, no fused multiply-add in the merge.  grid (query tiles, heads), 128 threads.

@@ -57,18 +57,21 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 // one CTA needs for one key tile (microseconds).
 constexpr long long kWaitLimitCycles = 2000000000LL;
 
-// Waits for the phase with the given parity to complete.  Gives up when the cycle budget is spent
+// Waits for the phase with the given parity to complete.  Gives up when the cycle limit is reached
 // or when another thread of the CTA has already raised *abort_flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, const volatile int* abort_flag, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 31u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) return false;
+      if (clock64() - t0 > limit_cycles) return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+  return mbar_wait_limited(bar, parity, abort_flag, kWaitLimitCycles);
 }
 
 // ---------------------------------------------------------------- TMA
