@@ -317,6 +317,14 @@ def main():
         barrier()
         ms_total = ev0.elapsed_time(ev1)
     launches = pkg.launch_count() - launches0
+    # the same steps once more with an event pair around each, for the spread (not part of `value`)
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in pairs:
+        a.record(stream)
+        step()
+        b.record(stream)
+    torch.cuda.synchronize()
+    per_launch = sorted(a.elapsed_time(b) for a, b in pairs)
     soak(0.25)
     clocks.__exit__(None, None, None)
     t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
@@ -388,7 +396,9 @@ def main():
                            "seed": args.seed,
                            "parallelism": f"{n_gpus} x whole workload, no collective"},
                 "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
-                "cpu_baseline": cpu, "pct_of_int8_peak": 100.0 * achieved / int8_peak}
+                "cpu_baseline": cpu, "pct_of_int8_peak": 100.0 * achieved / int8_peak,
+                "per_launch_ms": {"median": per_launch[len(per_launch) // 2], "min": per_launch[0], "max": per_launch[-1],
+                                  "note": "separate pass, one event pair per launch, L2 warm for workloads that fit in it"}}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
