@@ -96,6 +96,33 @@ def physical_gpu_index(local_rank):
     return local_rank
 
 
+def bind_host_thread_near_gpu(torch, local_rank):
+    """Moves this process onto the CPUs of the NUMA node the GPU hangs off, before any pinned host buffer
+    is allocated (pages are placed where they are first touched), so that with several ranks per host the
+    end-to-end copies do not all cross the socket interconnect.  Best effort: returns the node number, or
+    None when the topology cannot be read or no allowed CPU sits on that node."""
+    try:
+        prop = torch.cuda.get_device_properties(local_rank)
+        bdf = "%04x:%02x:%02x.0" % (prop.pci_domain_id, prop.pci_bus_id, prop.pci_device_id)
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            text = f.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
 def cpu_baseline(workload, seconds_hint=10.0):
     """The reference project's fp32 CPU path (its unchanged templates, one single-slice call chain per
     head, heads spread over all host threads) on a bounded sample of whole heads of `workload`."""
@@ -249,6 +276,7 @@ def main():
     args.warmup = max(args.warmup, 3)
 
     pkg.lib()  # fails loudly if the CUDA library is missing
+    host_numa = bind_host_thread_near_gpu(torch, local_rank) if world > 1 else None
     if args.path == "quantize":
         run_quantize_bench(args, pkg, w, dev, rank, world)
         return
@@ -394,7 +422,8 @@ def main():
                 "config": {"workload": f"{w.name}: B={w.B} H={w.H} S={w.S} D={w.D} per GPU", "mask": "none" if w.valid_choices is None else f"valid lengths {w.valid_choices}",
                            "l2": ("L2 overwritten between steps (Q,K,V,O = %.0f MB)" if flush_l2 else "inputs larger than L2 (Q,K,V,O = %.0f MB)") % (w.bytes / 1e6),
                            "seed": args.seed,
-                           "parallelism": f"{n_gpus} x whole workload, no collective"},
+                           "parallelism": f"{n_gpus} x whole workload, no collective",
+                           "host_numa_node_of_rank0": host_numa},
                 "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
                 "cpu_baseline": cpu, "pct_of_int8_peak": 100.0 * achieved / int8_peak,
                 "per_launch_ms": {"median": per_launch[len(per_launch) // 2], "min": per_launch[0], "max": per_launch[-1],
