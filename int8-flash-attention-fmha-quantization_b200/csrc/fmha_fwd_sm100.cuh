@@ -67,10 +67,10 @@ constexpr int kWarpScan = 10;         // prepares the next unit's mask informati
 // setmaxnreg moves registers inside the CTA's own launch allocation (registers per thread at launch x
 // threads), not inside the SM's whole register file: a request that does not fit blocks forever.  With
 // 384 threads the compiler's launch allocation is 168 registers per thread (the host checks this before
-// the first launch and refuses otherwise): 8 warps x 224 + 4 warps x 56 = 12 x 168.
+// the first launch and refuses otherwise): 8 warps x 208 + 4 warps x 88 = 12 x 168.
 constexpr int kLaunchRegs = 168;
-constexpr int kRegsSoftmax = 224;
-constexpr int kRegsOther = 56;
+constexpr int kRegsSoftmax = 208;
+constexpr int kRegsOther = 88;
 static_assert(8 * kRegsSoftmax + 4 * kRegsOther <= (kFwdThreads / 32) * kLaunchRegs,
               "setmaxnreg targets exceed the CTA's register allocation: the kernel would hang");
 constexpr uint32_t kTmemCols = 512;
@@ -117,7 +117,7 @@ struct UnitInfo {
 constexpr int kInfoConsumers = 10;    // loader, MMA issuer and the eight softmax warps each release an info buffer once
 
 template <int NS> struct FwdCtl {
-  uint64_t q_full, q_empty;
+  uint64_t q_full[2], q_empty[2];      // per query tile: its Q rows have landed / its last S = Q.K^T of the unit has completed
   uint64_t k_full[NS], k_empty[NS], v_full[NS], v_empty[NS];
   uint64_t s_full[2], p_ready[2], o_full[2], o_free[2];
   uint64_t info_full[2], info_empty[2];
@@ -496,21 +496,22 @@ __device__ __forceinline__ bool softmax_unit(const FwdParams& p, FwdCtl<FwdCfg<D
   if (ok && q_row < p.Sq) {
     const float inv = (n_live > 0 && l_run > 0.f) ? 1.0f / l_run : 0.f;
     int8_t* dst = p.o + (static_cast<int64_t>(bh_local) * p.Sq + q_row) * D;
+    // rn(clamp(x)) through the magic-number addition (the low byte of clamp(x) + 1.5*2^23 is the two's-complement
+    // integer), bytes gathered with PRMT: conversions and shifts would cost three times the issue cycles
+    const float2 inv2 = make_float2(inv, inv), sc2 = make_float2(p.scale_v_out, p.scale_v_out);
+    const float2 zero2 = make_float2(0.f, 0.f), magic2 = make_float2(kMagic, kMagic);
 #pragma unroll
     for (int c = 0; c < D / 16; ++c) {
       uint32_t wds[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
-        uint32_t b4 = 0;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 v2 = o2[(c * 16 + g * 4 + e) >> 1];
-          const float val = (e & 1) ? v2.y : v2.x;
-          const float fq = p.scale_v_out * (val * inv);
-          const int q8 = __float2int_rn(fmaxf(fminf(fq, 127.f), -127.f));
-          b4 |= (static_cast<uint32_t>(q8) & 0xFFu) << (8 * e);
-        }
-        wds[g] = b4;
+        float2 a = __ffma2_rn(sc2, __ffma2_rn(o2[c * 8 + g * 2], inv2, zero2), zero2);        // scale_v_out * (o * inv), each product rounded
+        float2 b = __ffma2_rn(sc2, __ffma2_rn(o2[c * 8 + g * 2 + 1], inv2, zero2), zero2);
+        a.x = fminf(fmaxf(a.x, -127.f), 127.f); a.y = fminf(fmaxf(a.y, -127.f), 127.f);
+        b.x = fminf(fmaxf(b.x, -127.f), 127.f); b.y = fminf(fmaxf(b.y, -127.f), 127.f);
+        const float2 ya = __fadd2_rn(a, magic2), yb = __fadd2_rn(b, magic2);
+        wds[g] = __byte_perm(__byte_perm(__float_as_uint(ya.x), __float_as_uint(ya.y), 0x0040),
+                             __byte_perm(__float_as_uint(yb.x), __float_as_uint(yb.y), 0x0040), 0x5410);
       }
       *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
     }
@@ -565,8 +566,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     ctl->abort = 0;
-    mbar_init(smem_u32(&ctl->q_full), 1);
-    mbar_init(smem_u32(&ctl->q_empty), 1);
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(smem_u32(&ctl->q_full[w]), 1);
+      mbar_init(smem_u32(&ctl->q_empty[w]), 1);
+    }
     for (int s = 0; s < NS; ++s) {
       mbar_init(smem_u32(&ctl->k_full[s]), 1);
       mbar_init(smem_u32(&ctl->k_empty[s]), 1);
@@ -630,7 +633,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // ---------------------------------------------------------------- loader
       if (lane == 0) {
         uint32_t kv_done = 0;      // key tiles loaded in earlier units: ring position and phase continue across units
-        uint32_t q_loads = 0;      // units with at least one live tile so far (phase of q_full / q_empty)
+        uint32_t q_loads[2] = {0u, 0u};   // Q tiles loaded so far per query-tile slot (phase of q_full[w] / q_empty[w])
         bool ok = true;
         int it = 0;
         for (int u = first_unit; u < p.n_units && ok; u += unit_step, ++it) {
@@ -642,13 +645,17 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const UnitInfo* info = &ctl->info[buf];
           const int n_live = info->n_live;
           if (n_live > 0) {
-            // the Q tiles of the previous unit are free once its last S = Q.K^T has completed
-            if (q_loads > 0 && !mbar_wait(smem_u32(&ctl->q_empty), (q_loads - 1) & 1u, abort_flag)) {
-              raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_FREE, it); ok = false; break;
+            // a slot's Q rows of the previous unit are free once that slot's last S = Q.K^T has completed
+            for (int w = 0; w < g.nq && ok; ++w) {
+              if (q_loads[w] > 0 && !mbar_wait(smem_u32(&ctl->q_empty[w]), (q_loads[w] - 1) & 1u, abort_flag)) {
+                raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_FREE, it); ok = false; break;
+              }
+              const uint32_t bar_q = smem_u32(&ctl->q_full[w]);
+              mbar_arrive_expect_tx(bar_q, static_cast<uint32_t>(Cfg::kTileBytes));
+              tma_load_3d(q_smem + w * Cfg::kTileBytes, &map_q, bar_q, 0, g.q_row0 + w * kTile, g.bh_local);
+              ++q_loads[w];
             }
-            const uint32_t bar_q = smem_u32(&ctl->q_full);
-            mbar_arrive_expect_tx(bar_q, static_cast<uint32_t>(g.nq * Cfg::kTileBytes));
-            for (int w = 0; w < g.nq; ++w) tma_load_3d(q_smem + w * Cfg::kTileBytes, &map_q, bar_q, 0, g.q_row0 + w * kTile, g.bh_local);
+            if (!ok) break;
             for (int j = 0; j < n_live; ++j) {
               const int t = info->live[j];
               const uint32_t gidx = kv_done + static_cast<uint32_t>(j);
@@ -665,7 +672,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               tma_load_3d(v_smem + s * Cfg::kTileBytes, &map_v, smem_u32(&ctl->v_full[s]), 0, t * kTile, g.bh_local);
             }
             kv_done += static_cast<uint32_t>(n_live);
-            ++q_loads;
           }
           mbar_arrive(smem_u32(&ctl->info_empty[buf]));
         }
@@ -703,9 +709,23 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         };
         uint32_t kv_done = 0;              // key tiles consumed in earlier units (ring position / phase)
         uint32_t tiles_done[2] = {0u, 0u}; // key tiles each query-tile slot has processed in earlier units
-        uint32_t q_loads = 0;              // units with at least one live tile seen so far (phase of q_full / q_empty)
+        uint32_t q_waits[2] = {0u, 0u};    // Q tiles each slot has waited for so far (phase of q_full[w])
+        bool pre[2] = {false, false};      // this unit's first S of slot w was already issued at the end of the previous unit
+        int first_s_count = 0;             // how many slots have issued the current (or, when looking ahead, next) unit's first S
         bool ok = true;
         int it = 0;
+        // First S = Q.K^T of a unit for slot w: key-tile stage s0 of a unit with n_live_u live tiles and nq_u query tiles.
+        auto first_s = [&](int w, uint32_t gidx0, int n_live_u, int nq_u) -> bool {
+          const uint32_t s0 = gidx0 % NS;
+          if (!mbar_wait(smem_u32(&ctl->q_full[w]), q_waits[w] & 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_Q_LOAD, w); return false; }
+          ++q_waits[w];
+          if (!mbar_wait(smem_u32(&ctl->k_full[s0]), (gidx0 / NS) & 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_LOAD, 0); return false; }
+          tc_fence_after();
+          issue_s(w, s0);
+          if (n_live_u == 1) mma_commit(smem_u32(&ctl->q_empty[w]));      // the unit's only use of this slot's Q
+          if (++first_s_count == nq_u) mma_commit(smem_u32(&ctl->k_empty[s0]));   // every slot has read this K stage
+          return true;
+        };
         for (int u = first_unit; u < p.n_units && ok; u += unit_step, ++it) {
           const int buf = it & 1;
           if (!mbar_wait(smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it >> 1) & 1), abort_flag)) {
@@ -714,16 +734,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const UnitGeom g = unit_geom(p, u);
           const int n_live = ctl->info[buf].n_live;
           const int nq = g.nq;
+          // what comes after this unit (looked at when a slot finishes its last tile here)
+          const int u_next = u + unit_step;
+          bool next_known = false;
+          int n_live_next = 0, nq_next = 0;
           if (n_live > 0) {
-            if (!mbar_wait(smem_u32(&ctl->q_full), q_loads & 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_Q_LOAD, it); ok = false; break; }
-            {
-              const uint32_t s0 = kv_done % NS;
-              if (!mbar_wait(smem_u32(&ctl->k_full[s0]), (kv_done / NS) & 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_LOAD, 0); ok = false; break; }
-              tc_fence_after();
-              for (int w = 0; w < nq; ++w) issue_s(w, s0);
-              mma_commit(smem_u32(&ctl->k_empty[s0]));
-              if (n_live == 1) mma_commit(smem_u32(&ctl->q_empty));
-            }
+            for (int w = 0; w < nq && ok; ++w)
+              if (!pre[w]) ok = first_s(w, kv_done, n_live, nq);
+            pre[0] = pre[1] = false;
+            first_s_count = 0;
             for (int j = 0; j < n_live && ok; ++j) {
               const uint32_t gidx = kv_done + static_cast<uint32_t>(j);
               const uint32_t s = gidx % NS;
@@ -745,16 +764,28 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                   tc_fence_after();
                   // S_w / P_w columns are free again: the tensor pipe runs this thread's MMAs in order
                   issue_s(w, sn);
-                  if (w == nq - 1) {
-                    mma_commit(smem_u32(&ctl->k_empty[sn]));
-                    if (j + 2 == n_live) mma_commit(smem_u32(&ctl->q_empty));    // that was the unit's last use of Q
+                  if (j + 2 == n_live) mma_commit(smem_u32(&ctl->q_empty[w]));   // that was the unit's last use of this slot's Q
+                  if (w == nq - 1) mma_commit(smem_u32(&ctl->k_empty[sn]));
+                } else if (u_next < p.n_units) {
+                  // This slot has finished the unit: start its first S of the NEXT unit now instead of when the other
+                  // slot has finished too, so the two slots keep their offset across unit boundaries.
+                  if (!next_known) {
+                    if (!mbar_wait(smem_u32(&ctl->info_full[buf ^ 1]), static_cast<uint32_t>(((it + 1) >> 1) & 1), abort_flag)) {
+                      raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_INFO, it + 1); ok = false; break;
+                    }
+                    n_live_next = ctl->info[buf ^ 1].n_live;
+                    nq_next = unit_geom(p, u_next).nq;
+                    next_known = true;
+                  }
+                  if (n_live_next > 0 && w < nq_next) {
+                    if (!first_s(w, kv_done + static_cast<uint32_t>(n_live), n_live_next, nq_next)) { ok = false; break; }
+                    pre[w] = true;
                   }
                 }
               }
             }
             kv_done += static_cast<uint32_t>(n_live);
             for (int w = 0; w < nq; ++w) tiles_done[w] += static_cast<uint32_t>(n_live);
-            ++q_loads;
           }
           mbar_arrive(smem_u32(&ctl->info_empty[buf]));
         }
