@@ -57,3 +57,34 @@ def test_more_slices_than_a_grid_dimension(pkg, oracle):
     heads = np.concatenate([[0, 1, B * H - 1, B * H - 2, 65535, 65536], rng.integers(0, B * H, 200)])
     rows = np.unique(np.concatenate([heads * S + r for r in (0, 17, 63)])).astype(np.int64)
     _check(pkg, oracle, torch, q8, k8, v8, mask, amax, rows, "B*H=70000")
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_many_units_per_cta_with_changing_shape_of_unit(pkg, oracle, D):
+    """384 work units on 148 persistent CTAs, so every CTA walks several units, and consecutive units of a CTA
+    differ in kind: S = 576 gives three query-tile pairs per head, the last with a single half-filled tile;
+    one batch is fully masked (units with no live key tile), one has 100 valid keys (one live tile), the rest
+    have random masks.  Every element against the CUDA-core cross-check, sampled rows against the CPU oracle."""
+    import torch
+    torch.cuda.set_device(0)
+    B, H, S = 4, 32, 576
+    q8, k8, v8, mask = _device_case(torch, B, H, S, D, seed=11 + D)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    mask[:] = (torch.rand((B, S), device="cuda", generator=g) < 0.2).to(torch.int8)
+    mask[1, :] = 1
+    mask[2, :] = 0
+    mask[2, 100:] = 1
+    amax = [0.1, 0.1, 1.0, 0.6]
+    for up in (False, True):
+        o8 = torch.full_like(q8, 0x5A)
+        pkg.FMHAInferI8(None, pkg.FMHAParamI8(*amax, 1.0), pkg.AttnDataDescriptor(B, S, H, D), q8, k8, v8, mask, o8, True, uint8_p=up)
+        chk = torch.empty_like(q8)
+        pkg.debug_simt_x(None, pkg.FMHAParamI8(*amax, 1.0), pkg.AttnDataDescriptorX(B, S, S, H, D), q8, k8, v8, mask, chk, uint8_p=up)
+        st, words = pkg.device_status()
+        assert st == pkg.OK, words
+        assert_parity(o8.cpu().numpy(), chk.cpu().numpy(), f"D={D} uint8_p={up} vs CUDA-core kernel")
+        assert bool((o8[1] == 0).all())
+        rows = sample_rows(B, H, S, 6, seed=D)
+        want = oracle.q128(q8.cpu().numpy(), k8.cpu().numpy(), v8.cpu().numpy(), mask.cpu().numpy(), amax, rows=rows,
+                           p_levels=255 if up else 128)
+        assert_parity(o8.view(-1, D)[torch.from_numpy(rows).cuda()].cpu().numpy(), want, f"D={D} uint8_p={up} vs oracle")
