@@ -368,11 +368,21 @@ int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void*
   // chunk i-1 on its way out (the bus is full duplex).  Each chunk is one fmha_i8_sm100_infer_slice.
   const int BH = desc[0] * desc[2];
   const int n_chunks = BH < kHostChunks ? BH : kHostChunks;
+  // The inbound copies are the bottleneck, so what follows the last of them -- the last chunk's kernel and its
+  // outbound copy -- is exposed: with enough heads the last chunk is made small (1/24 of the heads) and the
+  // others share the rest equally.
+  int bounds[kHostChunks + 1];
+  {
+    const int tail = (BH >= 8 * kHostChunks) ? (BH / 24 > 0 ? BH / 24 : 1) : 0;      // 0: equal chunks
+    const int body = BH - tail, n_body = tail ? n_chunks - 1 : n_chunks;
+    for (int i = 0; i <= n_body; ++i) bounds[i] = static_cast<int>(static_cast<long long>(body) * i / n_body);
+    if (tail) bounds[n_chunks] = BH;
+  }
   const size_t head_bytes = static_cast<size_t>(desc[1]) * desc[3];
   cudaError_t e = cudaMemcpyAsync(s.mask, host_mask, mask_bytes, cudaMemcpyHostToDevice, s.s_in);
   for (int i = 0; i < n_chunks && e == cudaSuccess; ++i) {
-    const int begin = static_cast<int>(static_cast<long long>(BH) * i / n_chunks);
-    const int end = static_cast<int>(static_cast<long long>(BH) * (i + 1) / n_chunks);
+    const int begin = bounds[i];
+    const int end = bounds[i + 1];
     const size_t off = begin * head_bytes, bytes = (end - begin) * head_bytes;
     const char* hq = static_cast<const char*>(host_q) + off;
     const char* hk = static_cast<const char*>(host_k) + off;
