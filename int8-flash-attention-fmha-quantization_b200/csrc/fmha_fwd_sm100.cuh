@@ -717,12 +717,21 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         int first_s_count = 0;             // how many slots have issued the current (or, when looking ahead, next) unit's first S
         bool ok = true;
         int it = 0;
+        // A wait that gives up only notes which one it was; the status is raised once, after the loops, so that the
+        // loops contain no calls (every call site would cost this register-starved thread spills around it).
+        uint32_t err = 0u, err_tile = 0u;
+        auto wait = [&](uint32_t bar, uint32_t parity, uint32_t code, uint32_t tile) -> bool {
+          if (mbar_wait(bar, parity, abort_flag)) return true;
+          err = code;
+          err_tile = tile;
+          return false;
+        };
         // First S = Q.K^T of a unit for slot w: key-tile stage s0 of a unit with n_live_u live tiles and nq_u query tiles.
         auto first_s = [&](int w, uint32_t gidx0, int n_live_u, int nq_u) -> bool {
           const uint32_t s0 = gidx0 % NS;
-          if (!mbar_wait(smem_u32(&ctl->q_full[w]), q_waits[w] & 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_Q_LOAD, w); return false; }
+          if (!wait(smem_u32(&ctl->q_full[w]), q_waits[w] & 1u, FMHA_I8_DEV_WAIT_Q_LOAD, w)) return false;
           ++q_waits[w];
-          if (!mbar_wait(smem_u32(&ctl->k_full[s0]), (gidx0 / NS) & 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_LOAD, 0); return false; }
+          if (!wait(smem_u32(&ctl->k_full[s0]), (gidx0 / NS) & 1u, FMHA_I8_DEV_WAIT_K_LOAD, 0)) return false;
           tc_fence_after();
           issue_s(w, s0);
           if (n_live_u == 1) mma_commit(smem_u32(&ctl->q_empty[w]));      // the unit's only use of this slot's Q
@@ -731,9 +740,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         };
         for (int u = first_unit; u < p.n_units && ok; u += unit_step, ++it) {
           const int buf = it & 1;
-          if (!mbar_wait(smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it >> 1) & 1), abort_flag)) {
-            raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_INFO, it); ok = false; break;
-          }
+          if (!wait(smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it >> 1) & 1), FMHA_I8_DEV_WAIT_INFO, it)) { ok = false; break; }
           const UnitGeom g = unit_geom(p, u);
           const int n_live = ctl->info[buf].n_live;
           const int nq = g.nq;
@@ -749,40 +756,47 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             for (int j = 0; j < n_live && ok; ++j) {
               const uint32_t gidx = kv_done + static_cast<uint32_t>(j);
               const uint32_t s = gidx % NS;
-              if (!mbar_wait(smem_u32(&ctl->v_full[s]), (gidx / NS) & 1u, abort_flag)) {
-                raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_V_LOAD, j); ok = false; break;
-              }
+              if (!wait(smem_u32(&ctl->v_full[s]), (gidx / NS) & 1u, FMHA_I8_DEV_WAIT_V_LOAD, j)) { ok = false; break; }
               const uint32_t gn = gidx + 1, sn = gn % NS;
               for (int w = 0; w < nq; ++w) {
                 const uint32_t tw = tiles_done[w] + static_cast<uint32_t>(j);     // this slot's cumulative tile index
-                if (!mbar_wait(smem_u32(&ctl->p_ready[w]), tw & 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_P_READY, j); ok = false; break; }
-                if (tw > 0 && !mbar_wait(smem_u32(&ctl->o_free[w]), (tw - 1) & 1u, abort_flag)) { raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_O_FREE, j); ok = false; break; }
+                if (!wait(smem_u32(&ctl->p_ready[w]), tw & 1u, FMHA_I8_DEV_WAIT_P_READY, j)) { ok = false; break; }
+                if (tw > 0 && !wait(smem_u32(&ctl->o_free[w]), (tw - 1) & 1u, FMHA_I8_DEV_WAIT_O_FREE, j)) { ok = false; break; }
                 tc_fence_after();
                 issue_o(w, s);
                 if (w == nq - 1) mma_commit(smem_u32(&ctl->v_empty[s]));
-                if (j + 1 < n_live) {
-                  if (w == 0 && !mbar_wait(smem_u32(&ctl->k_full[sn]), (gn / NS) & 1u, abort_flag)) {
-                    raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_LOAD, j + 1); ok = false; break;
-                  }
-                  tc_fence_after();
-                  // S_w / P_w columns are free again: the tensor pipe runs this thread's MMAs in order
-                  issue_s(w, sn);
-                  if (j + 2 == n_live) mma_commit(smem_u32(&ctl->q_empty[w]));   // that was the unit's last use of this slot's Q
-                  if (w == nq - 1) mma_commit(smem_u32(&ctl->k_empty[sn]));
-                } else if (u_next < p.n_units) {
-                  // This slot has finished the unit: start its first S of the NEXT unit now instead of when the other
-                  // slot has finished too, so the two slots keep their offset across unit boundaries.
+                // ---- this slot's next S = Q.K^T: the next key tile of this unit, or -- after the unit's last tile --
+                //      the first key tile of the NEXT unit, started now rather than when the other slot has finished
+                //      too, so that the two slots keep their offset across unit boundaries
+                bool cross = false, have_next = (j + 1 < n_live);
+                uint32_t g_next = gidx + 1;
+                if (!have_next && u_next < p.n_units) {
                   if (!next_known) {
-                    if (!mbar_wait(smem_u32(&ctl->info_full[buf ^ 1]), static_cast<uint32_t>(((it + 1) >> 1) & 1), abort_flag)) {
-                      raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_INFO, it + 1); ok = false; break;
-                    }
+                    if (!wait(smem_u32(&ctl->info_full[buf ^ 1]), static_cast<uint32_t>(((it + 1) >> 1) & 1), FMHA_I8_DEV_WAIT_INFO, it + 1)) { ok = false; break; }
                     n_live_next = ctl->info[buf ^ 1].n_live;
                     nq_next = unit_geom(p, u_next).nq;
                     next_known = true;
                   }
-                  if (n_live_next > 0 && w < nq_next) {
-                    if (!first_s(w, kv_done + static_cast<uint32_t>(n_live), n_live_next, nq_next)) { ok = false; break; }
+                  cross = have_next = (n_live_next > 0 && w < nq_next);
+                }
+                if (have_next) {
+                  const uint32_t s_next = g_next % NS;
+                  if (cross) {
+                    if (!wait(smem_u32(&ctl->q_full[w]), q_waits[w] & 1u, FMHA_I8_DEV_WAIT_Q_LOAD, w)) { ok = false; break; }
+                    ++q_waits[w];
+                  }
+                  if ((cross || w == 0) && !wait(smem_u32(&ctl->k_full[s_next]), (g_next / NS) & 1u, FMHA_I8_DEV_WAIT_K_LOAD, j + 1)) { ok = false; break; }
+                  tc_fence_after();
+                  // S_w / P_w columns are free again: the tensor pipe runs this thread's MMAs in order
+                  issue_s(w, s_next);
+                  // that was the unit's last use of this slot's Q rows?
+                  if (cross ? (n_live_next == 1) : (j + 2 == n_live)) mma_commit(smem_u32(&ctl->q_empty[w]));
+                  // has every slot read this K stage?
+                  if (cross) {
                     pre[w] = true;
+                    if (++first_s_count == nq_next) mma_commit(smem_u32(&ctl->k_empty[s_next]));
+                  } else if (w == nq - 1) {
+                    mma_commit(smem_u32(&ctl->k_empty[s_next]));
                   }
                 }
               }
@@ -792,6 +806,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
           mbar_arrive(smem_u32(&ctl->info_empty[buf]));
         }
+        if (err != 0u) raise_status(abort_flag, p.status, err, err_tile);
       }
     } else if (warp == kWarpScan) {
       // ---------------------------------------------------------------- scanner: mask information, one unit ahead
