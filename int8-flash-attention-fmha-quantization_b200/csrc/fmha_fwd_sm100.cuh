@@ -67,12 +67,17 @@ constexpr int kWarpScan = 10;         // prepares the next unit's mask informati
 // setmaxnreg moves registers inside the CTA's own launch allocation (registers per thread at launch x
 // threads), not inside the SM's whole register file: a request that does not fit blocks forever.  With
 // 384 threads the compiler's launch allocation is 168 registers per thread (the host checks this before
-// the first launch and refuses otherwise): 8 warps x 208 + 4 warps x 88 = 12 x 168.
+// the first launch and refuses otherwise).  head_dim 128: 8 warps x 208 + 4 warps x 88 = 12 x 168 (the
+// softmax warps hold a 128-register output row; the MMA issuer needs more than the 56 a 224/56 split would
+// leave it).  head_dim 64: nobody needs more than 168, so nothing is moved (measured: C5 +5 % against 208/88).
 constexpr int kLaunchRegs = 168;
-constexpr int kRegsSoftmax = 208;
-constexpr int kRegsOther = 88;
-static_assert(8 * kRegsSoftmax + 4 * kRegsOther <= (kFwdThreads / 32) * kLaunchRegs,
-              "setmaxnreg targets exceed the CTA's register allocation: the kernel would hang");
+template <int D> struct FwdRegs {
+  static constexpr int kSoftmax = (D == 128) ? 208 : kLaunchRegs;
+  static constexpr int kOther = (D == 128) ? 88 : kLaunchRegs;
+  static_assert(8 * kSoftmax + 4 * kOther <= (kFwdThreads / 32) * kLaunchRegs,
+                "setmaxnreg targets exceed the CTA's register allocation: the kernel would hang");
+  static_assert(kSoftmax >= kLaunchRegs && kOther <= kLaunchRegs, "softmax warps only gain, the others only give");
+};
 constexpr uint32_t kTmemCols = 512;
 constexpr float kMagic = 12582912.0f;          // 1.5 * 2^23: float whose ulp is 1 over [2^23, 2^24)
 constexpr uint32_t kMagicBits = 0x4B400000u;
@@ -608,7 +613,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   // phase of an info barrier for unit `it` is (it >> 1) & 1.
   if (warp < 8) {
     // ------------------------------------------------------------------ softmax groups
-    setmaxnreg_inc<kRegsSoftmax>();
+    setmaxnreg_inc<FwdRegs<D>::kSoftmax>();      // (a request equal to the launch allocation changes nothing)
     const int w = warp >> 2;
     const int row_in_tile = (warp & 3) * 32 + lane;
     uint32_t tiles_done = 0;
@@ -631,7 +636,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (!ok) break;
     }
   } else {
-    setmaxnreg_dec<kRegsOther>();
+    setmaxnreg_dec<FwdRegs<D>::kOther>();
     if (warp == kWarpLoad) {
       // ---------------------------------------------------------------- loader
       if (lane == 0) {
