@@ -33,6 +33,9 @@ constexpr int kMaxDevices = 64;
 struct DeviceInfo {
   int checked = 0;      // 0 = not yet, 1 = sm_100, -1 = something else
   unsigned* status = nullptr;
+  // One word of mapped, pinned host memory per device.  A kernel whose bounded wait runs out writes 1 to
+  // it (besides the device status words), so the next host call can see the failure without synchronising.
+  volatile unsigned* host_flag = nullptr;
   int sm_count = 0;
   bool attr_set = false;
 };
@@ -60,13 +63,29 @@ DeviceInfo* current_device(int* err) {
   if (!d.status) {
     void* ptr = nullptr;
     if (cudaGetSymbolAddress(&ptr, g_status_words) != cudaSuccess) { *err = FMHA_I8_ERR_LAUNCH; return nullptr; }
+    // the host-visible failure word (set-up only: a few bytes of pinned host memory, nothing on the device)
+    void* host_word = nullptr;
+    void* dev_view = nullptr;
+    if (cudaHostAlloc(&host_word, sizeof(unsigned), cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer(&dev_view, host_word, 0) != cudaSuccess) {
+      cudaGetLastError();
+      *err = FMHA_I8_ERR_LAUNCH;
+      return nullptr;
+    }
+    *static_cast<volatile unsigned*>(host_word) = 0u;
+    if (cudaMemcpyToSymbol(g_host_flag_ptr, &dev_view, sizeof(dev_view)) != cudaSuccess) {
+      cudaGetLastError();
+      *err = FMHA_I8_ERR_LAUNCH;
+      return nullptr;
+    }
+    d.host_flag = static_cast<volatile unsigned*>(host_word);
     d.status = static_cast<unsigned*>(ptr);
   }
   return &d;
 }
 
 template <int D> size_t fwd_smem_bytes() {
-  return 1024 + FwdCfg<D>::kTilesBytesTotal + 2 * kBiasBytes + sizeof(FwdCtl<FwdCfg<D>::kStages>);
+  return 1024 + FwdCfg<D>::kTilesBytesTotal + 2 * kBiasBytes + sizeof(FwdCtl<FwdCfg<D>::kStagesK, FwdCfg<D>::kStagesV>);
 }
 template <int D> size_t qk_smem_bytes() { return 1024 + 2 * kTile * D + sizeof(DebugCtl); }
 template <int D> size_t pv_smem_bytes() { return 1024 + kTile * D + kTile * kTile + sizeof(DebugCtl); }
@@ -88,6 +107,7 @@ int set_kernel_attributes(DeviceInfo* d) {
   if (e != cudaSuccess) { cudaGetLastError(); return FMHA_I8_ERR_LAUNCH; }
   // The forward kernel redistributes registers with setmaxnreg; that only terminates if the launch
   // allocation is the one the targets were sized for.
+  static_assert(FwdRegs::kMerge <= 255, "register targets");
   cudaFuncAttributes fa64{}, fa128{};
   if (cudaFuncGetAttributes(&fa64, reinterpret_cast<const void*>(&fmha_fwd_kernel<64>)) != cudaSuccess ||
       cudaFuncGetAttributes(&fa128, reinterpret_cast<const void*>(&fmha_fwd_kernel<128>)) != cudaSuccess ||
@@ -217,6 +237,12 @@ int infer_x_impl(void* stream, const float amax[5], const Shape& sh, const void*
   DeviceInfo* dev = current_device(&err);
   if (!dev) return err;
   if ((st = set_kernel_attributes(dev)) != FMHA_I8_OK) return st;
+  // A kernel launched earlier gave up on a bounded wait (its output is invalid): say so ONCE, on the first call
+  // that can see it, without launching; the details stay in the status words until fmha_i8_sm100_device_status().
+  if (*dev->host_flag != 0u) {
+    *dev->host_flag = 0u;
+    return FMHA_I8_ERR_DEVICE;
+  }
   p.mask = static_cast<const int8_t*>(mask);
   p.o = static_cast<int8_t*>(o);
   p.S = sh.Sk;
@@ -224,9 +250,9 @@ int infer_x_impl(void* stream, const float amax[5], const Shape& sh, const void*
   p.H = sh.H;
   p.bh_begin = bh_begin;
   p.bh_count = bh_count;
-  p.q_pairs = (p.Sq + 2 * kTile - 1) / (2 * kTile);
+  p.q_tiles = (p.Sq + kTile - 1) / kTile;
   {
-    const long long units = static_cast<long long>(bh_count) * p.q_pairs;
+    const long long units = static_cast<long long>(bh_count) * p.q_tiles;
     if (units > 0x7FFFFFFFLL) return FMHA_I8_ERR_BAD_SHAPE;
     p.n_units = static_cast<int>(units);
   }
@@ -253,7 +279,7 @@ struct HostStaging {
   bool ready = false;
 };
 HostStaging g_staging[kMaxDevices];
-std::mutex g_staging_mutex;
+std::mutex g_staging_mutex[kMaxDevices];     // one lock per device: host threads that drive different GPUs do not wait for each other
 
 // Scratch of fmha_i8_sm100_quantize_f32 (partial maxima), one buffer per device, grown on demand.
 struct QuantScratch {
@@ -331,10 +357,10 @@ int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void*
   int st = check_shape(desc);
   if (st != FMHA_I8_OK) return finish(st);
   int dev_id = 0;
-  if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id >= kMaxDevices) return finish(FMHA_I8_ERR_LAUNCH);
+  if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= kMaxDevices) return finish(FMHA_I8_ERR_LAUNCH);
   const size_t tensor_bytes = static_cast<size_t>(desc[0]) * desc[2] * desc[1] * desc[3];
   const size_t mask_bytes = static_cast<size_t>(desc[0]) * desc[1];
-  std::lock_guard<std::mutex> lock(g_staging_mutex);
+  std::lock_guard<std::mutex> lock(g_staging_mutex[dev_id]);
   HostStaging& s = g_staging[dev_id];
   if (!s.ready) {
     bool good = cudaStreamCreateWithFlags(&s.s_in, cudaStreamNonBlocking) == cudaSuccess &&
@@ -516,20 +542,18 @@ int fmha_i8_sm100_quantize_f32(void* stream, const float* x, long long n, int8_t
   cudaGetDevice(&dev_id);
   const long long n_chunks = (n + kQuantChunk - 1) / kQuantChunk;
   if (n_chunks > 0x7FFFFFFFLL) return finish(FMHA_I8_ERR_TOO_LARGE);
-  float* partial = nullptr;
-  {
-    std::lock_guard<std::mutex> lock(g_quant_mutex);
-    QuantScratch& q = g_quant_scratch[dev_id];
-    if (q.capacity_chunks < n_chunks) {
-      // growing frees the old buffer: wait for work that may still read it
-      if (q.partial) { cudaDeviceSynchronize(); cudaFree(q.partial); q.partial = nullptr; q.capacity_chunks = 0; }
-      const long long cap = n_chunks < 4096 ? 4096 : n_chunks;
-      if (cudaMalloc(&q.partial, sizeof(float) * cap) != cudaSuccess) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
-      q.capacity_chunks = cap;
-    }
-    partial = q.partial;
+  // The lock is held until the kernels are enqueued: another host thread that has to grow the scratch
+  // synchronises the device before it frees the old buffer, and that only covers work already enqueued.
+  std::lock_guard<std::mutex> lock(g_quant_mutex);
+  QuantScratch& q = g_quant_scratch[dev_id];
+  if (q.capacity_chunks < n_chunks) {
+    // growing frees the old buffer: wait for work that may still read it
+    if (q.partial) { cudaDeviceSynchronize(); cudaFree(q.partial); q.partial = nullptr; q.capacity_chunks = 0; }
+    const long long cap = n_chunks < 4096 ? 4096 : n_chunks;
+    if (cudaMalloc(&q.partial, sizeof(float) * cap) != cudaSuccess) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
+    q.capacity_chunks = cap;
   }
-  return finish(launch_quantize(static_cast<cudaStream_t>(stream), x, n, out, amax_out, partial, n_chunks));
+  return finish(launch_quantize(static_cast<cudaStream_t>(stream), x, n, out, amax_out, q.partial, n_chunks));
 }
 
 int fmha_i8_sm100_quantize_f32_noalloc(void* stream, const float* x, long long n, int8_t* out, float* amax_out) {
@@ -571,6 +595,13 @@ int fmha_i8_sm100_device_status(unsigned words[8]) {
   if (cudaMemcpyFromSymbol(words, g_status_words, sizeof(unsigned) * 8) != cudaSuccess) return finish(FMHA_I8_ERR_LAUNCH);
   const unsigned zeros[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (cudaMemcpyToSymbol(g_status_words, zeros, sizeof zeros) != cudaSuccess) return finish(FMHA_I8_ERR_LAUNCH);
+  {
+    int dev_id = 0;
+    if (cudaGetDevice(&dev_id) == cudaSuccess && dev_id >= 0 && dev_id < kMaxDevices) {
+      std::lock_guard<std::mutex> lock(g_dev_mutex);
+      if (g_dev[dev_id].host_flag) *g_dev[dev_id].host_flag = 0u;
+    }
+  }
   return finish(words[0] == 0u ? FMHA_I8_OK : FMHA_I8_ERR_DEVICE);
 }
 
@@ -603,7 +634,7 @@ int fmha_i8_sm100_version(void) { return 100; }
 // Performance-work builds only: copies out the timeline stamps of the first CTA.
 int fmha_i8_sm100_read_trace(long long* out) {
   if (cudaDeviceSynchronize() != cudaSuccess) return FMHA_I8_ERR_LAUNCH;
-  return cudaMemcpyFromSymbol(out, fmha::g_trace, sizeof(long long) * 16 * 512) == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH;
+  return cudaMemcpyFromSymbol(out, fmha::g_trace, sizeof(long long) * 48 * 512) == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH;
 }
 #endif
 

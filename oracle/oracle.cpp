@@ -263,6 +263,123 @@ void oracle_q128(const int8_t* q, const int8_t* k, const int8_t* v, const int8_t
   oracle_q128_x(q, k, v, mask, B, H, S, S, D, amax, 128, rows, n_rows, out, n_threads);
 }
 
+// Emulation of the reference CUDA kernel AS WRITTEN (inc/fmha_i8.cuh:87-332, the 128-key-tile variants), thread
+// for thread where it matters, for pinning tier C against bytes the reference kernel really produces.
+// It differs from tier C in exactly two places, both selectable so that each difference can be shown on its own:
+//
+//   mask_minus_1e6 != 0  a masked key enters the tile maximum as int(-1e6) before scaling (:191-193) and tiles whose
+//                        keys are all masked are still processed (tier C: masked keys never enter the maximum,
+//                        such tiles are skipped);
+//   shuffle_as_written != 0  the accumulator-to-A-operand relayout of P (:239-253) is reproduced with the semantics
+//                        CUDA gives __shfl_sync: every lane PUBLISHES p_fp32_frag[xi].x[which_val_idx] computed from
+//                        ITS OWN lane id, and receives what lane `which_lane_x` published.  The index the receiving
+//                        lane computed is only right when the publishing lane sits in the same half of the quad
+//                        (lane%4 in {0,1} vs {2,3}), so within every block of 16 keys the A operand ends up holding
+//                        P columns {0-3, 12-15, 0-3, 12-15} instead of {0-15}: keys 4-11 of each block are dropped
+//                        from P.V and keys 0-3 and 12-15 counted twice, while the row sum still counts every key
+//                        once.  (shuffle_as_written == 0: the relayout the code intends, identity.)
+//
+// Assumed register layouts (the ones the reference's index arithmetic assumes, :183-196): accumulator element
+// x[tc_xi*4 + tc_yi*2 + e] of lane L is (row L/4 + 8 tc_yi, column 8 tc_xi + 2 (L%4) + e); matrix_a int8 element
+// x[tc_yi*4 + t] of lane L is (row L/4 + 8 tc_yi, column 4 (L%4) + t).
+// Summation orders follow the kernel (per-lane partial sums over its 4 columns of each block, then the xor-2 / xor-1
+// butterfly); expf stands in for __expf and 1/x for __frcp_rn.  S must be a multiple of 128.
+void oracle_refkernel_emulate(const int8_t* q, const int8_t* k, const int8_t* v, const int8_t* mask,
+                              int B, int H, int S, int D, const float* amax, int mask_minus_1e6, int shuffle_as_written,
+                              int8_t* out, int n_threads) {
+  const float row_scale = 1.0f / newton_sqrt(static_cast<float>(D));          // fmha_i8.cuh:71
+  const float scale_qk = amax[0] * amax[1] / (127.f * 127.f);                  // fmha_i8.cuh:72
+  const float scale_v_out = amax[2] * (1.0f / (amax[3] * 128.f));             // fmha_i8.cuh:318
+  // column of P (within a block of 16 keys) that lands in A-operand column a
+  int perm[16];
+  for (int a = 0; a < 16; ++a) {
+    if (!shuffle_as_written) { perm[a] = a; continue; }
+    const int lane_x = a / 4, tc_xi = a % 4;                                   // receiving lane (within its quad) and loop index
+    const int c = lane_x * 4 + tc_xi;                                          // the column it wants (:246)
+    const int src = (c % 8) / 2;                                               // which_lane_x (:246)
+    const int src_idx = (src * 4 + tc_xi) / 8 * 4 + tc_xi % 2;                 // which_val_idx evaluated BY THE SOURCE lane (:247), without tc_yi*2
+    perm[a] = 8 * (src_idx / 4) + 2 * src + (src_idx % 2);                     // accumulator layout: column of x[src_idx] in lane src
+  }
+  const int64_t total = static_cast<int64_t>(B) * H * S;
+  const int chunks = static_cast<int>(std::min<int64_t>(total, 4096));
+  parallel_for(chunks, n_threads, [=](int c0) {
+    std::vector<float> sf(128), pf(128), o(D);
+    std::vector<int32_t> ot(D), sraw(128);
+    int32_t p8[128];
+    for (int64_t r = c0; r < total; r += chunks) {
+      const int64_t bh = r / S;
+      const int i = static_cast<int>(r % S);
+      const int b = static_cast<int>(bh / H);
+      const int8_t* qr = q + (bh * S + i) * D;
+      const int8_t* kb = k + bh * S * D;
+      const int8_t* vb = v + bh * S * D;
+      const int8_t* mb = mask + static_cast<int64_t>(b) * S;
+      float m_run = -1e6f, l_run = 0.f;                                        // fmha_i8.cuh:91-92
+      std::fill(o.begin(), o.end(), 0.f);
+      for (int j0 = 0; j0 < S; j0 += 128) {
+        if (!mask_minus_1e6) {
+          bool any = false;
+          for (int c2 = 0; c2 < 128; ++c2) any |= (mb[j0 + c2] == 0);
+          if (!any) continue;
+        }
+        for (int c2 = 0; c2 < 128; ++c2) {
+          int32_t acc = 0;
+          const int8_t* kr = kb + static_cast<int64_t>(j0 + c2) * D;
+          for (int d = 0; d < D; ++d) acc += static_cast<int32_t>(qr[d]) * static_cast<int32_t>(kr[d]);
+          sraw[c2] = acc;
+        }
+        // tile maximum (:183-206): pairs of columns, masked values replaced before scaling
+        float m_t = mask_minus_1e6 ? -1e6f : -INFINITY;
+        for (int c2 = 0; c2 < 128; c2 += 2) {
+          if (mask_minus_1e6) {
+            const int v1 = mb[j0 + c2] ? static_cast<int>(-1e6) : sraw[c2];
+            const int v2 = mb[j0 + c2 + 1] ? static_cast<int>(-1e6) : sraw[c2 + 1];
+            m_t = std::max(m_t, row_scale * static_cast<float>(std::max(v1, v2)) * scale_qk);
+          } else {
+            if (!mb[j0 + c2]) m_t = std::max(m_t, row_scale * static_cast<float>(sraw[c2]) * scale_qk);
+            if (!mb[j0 + c2 + 1]) m_t = std::max(m_t, row_scale * static_cast<float>(sraw[c2 + 1]) * scale_qk);
+          }
+        }
+        // probabilities and the row sum in the kernel's order (:208-235): lane L of the quad owns columns
+        // 16 xi + 8 tc_xi + 2 L + {0,1}; partial sums per lane, then (s0 + s2) + (s1 + s3)
+        float lane_sum[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int xi = 0; xi < 8; ++xi)
+          for (int tc_xi = 0; tc_xi < 2; ++tc_xi)
+            for (int L = 0; L < 4; ++L) {
+              const int c2 = 16 * xi + 8 * tc_xi + 2 * L;
+              const float e0 = expf(row_scale * static_cast<float>(sraw[c2]) * scale_qk - m_t);
+              const float e1 = expf(row_scale * static_cast<float>(sraw[c2 + 1]) * scale_qk - m_t);
+              pf[c2] = mb[j0 + c2] ? 0.f : e0;
+              pf[c2 + 1] = mb[j0 + c2 + 1] ? 0.f : e1;
+              lane_sum[L] += (pf[c2] + pf[c2 + 1]);
+            }
+        const float l_t = (lane_sum[0] + lane_sum[2]) + (lane_sum[1] + lane_sum[3]);
+        for (int c2 = 0; c2 < 128; ++c2)                                         // :241-250
+          p8[c2] = clamp_round_even_i32(-128.f * pf[c2], -128.f, 0.f);
+        std::fill(ot.begin(), ot.end(), 0);
+        for (int xi = 0; xi < 8; ++xi)
+          for (int a = 0; a < 16; ++a) {
+            const int pv = p8[16 * xi + perm[a]];
+            if (pv == 0) continue;
+            const int8_t* vr = vb + static_cast<int64_t>(j0 + 16 * xi + a) * D;
+            for (int d = 0; d < D; ++d) ot[d] += pv * static_cast<int32_t>(vr[d]);
+          }
+        const float m_new = std::max(m_run, m_t);                              // :301-310
+        const float e_old = expf(m_run - m_new);
+        const float e_cur = expf(m_t - m_new);
+        const float l_new = e_old * l_run + e_cur * l_t;
+        const float rcp = 1.0f / l_new;
+        for (int d = 0; d < D; ++d)
+          o[d] = rcp * (l_run * e_old * o[d] + e_cur * (-1.f * static_cast<float>(ot[d])));
+        l_run = l_new;
+        m_run = m_new;
+      }
+      int8_t* dst = out + r * D;
+      for (int d = 0; d < D; ++d) dst[d] = clamp_round_even(scale_v_out * o[d], -127.f, 127.f);  // :327-328
+    }
+  });
+}
+
 // The constant the device kernel and tier C share for 1/sqrt(head_dim).
 float oracle_row_scale(int D) { return 1.0f / newton_sqrt(static_cast<float>(D)); }
 

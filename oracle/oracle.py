@@ -20,13 +20,24 @@ _i8p = np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS")
 _i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
 
 
+def reference_checkout():
+    """Directory of a checkout of the reference project, or None.  Taken from the environment variable
+    FMHA_REFERENCE_DIR, else from a directory named `reference` beside this repository."""
+    cands = [os.environ.get("FMHA_REFERENCE_DIR"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "inc", "cpuGEMM.hpp")):
+            return c
+    return None
+
+
 def build(force=False):
     """Compile liboracle.so (and oracle/_ref when a reference checkout is present)."""
     lib = os.path.join(HERE, "liboracle.so")
     if force or not os.path.exists(lib) or os.path.getmtime(lib) < os.path.getmtime(os.path.join(HERE, "oracle.cpp")):
         subprocess.check_call(["make", "-s", "-C", HERE, os.path.join(HERE, "liboracle.so")])
-    if os.path.exists("/root/reference/inc/cpuGEMM.hpp"):
-        subprocess.call(["make", "-s", "-C", HERE, "ref"])
+    ref = reference_checkout()
+    if ref:
+        subprocess.call(["make", "-s", "-C", HERE, "ref", "REF=" + ref])
     return lib
 
 
@@ -54,6 +65,8 @@ def lib():
                                               _f32p, _c.POINTER(_c.c_float), _c.c_int]
         L.oracle_q128_x.argtypes = [_i8p, _i8p, _i8p, _i8p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _f32p,
                                     _c.c_int, _c.c_void_p, _c.c_int64, _i8p, _c.c_int]
+        L.oracle_refkernel_emulate.argtypes = [_i8p, _i8p, _i8p, _i8p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _f32p,
+                                               _c.c_int, _c.c_int, _i8p, _c.c_int]
         L.oracle_row_scale.restype = _c.c_float
         L.oracle_row_scale.argtypes = [_c.c_int]
         _lib = L
@@ -142,6 +155,22 @@ def ref_cpu_available(native=False):
     return os.path.exists(os.path.join(HERE, "_ref", "libref_cpu_native.so" if native else "libref_cpu.so"))
 
 
+def refkernel_emulate(q8, k8, v8, mask, amax4, mask_minus_1e6=True, shuffle_as_written=True, threads=None):
+    """CPU emulation of the reference CUDA kernel as written (inc/fmha_i8.cuh:87-332, 128-key tiles): tier C's
+    arithmetic plus the kernel's own treatment of masked keys (int(-1e6) before scaling) and its P relayout with
+    the semantics __shfl_sync really has.  Either departure can be switched off.  int8 [B,H,S,D], S % 128 == 0."""
+    B, H, S, D = q8.shape
+    assert S % 128 == 0 and k8.shape == q8.shape and v8.shape == q8.shape and mask.shape == (B, S)
+    a = np.asarray(amax4, np.float32)
+    assert a.size == 4
+    out = np.empty((B, H, S, D), np.int8)
+    lib().oracle_refkernel_emulate(np.ascontiguousarray(q8, np.int8), np.ascontiguousarray(k8, np.int8),
+                                   np.ascontiguousarray(v8, np.int8), np.ascontiguousarray(mask, np.int8), B, H, S, D, a,
+                                   1 if mask_minus_1e6 else 0, 1 if shuffle_as_written else 0, out,
+                                   threads or n_threads_default())
+    return out
+
+
 def ref_gpu_available():
     return os.path.exists(os.path.join(HERE, "_ref", "libref_gpu.so"))
 
@@ -208,5 +237,7 @@ def ref_gpu():
         L = ctypes.CDLL(os.path.join(HERE, "_ref", "libref_gpu.so"))
         L.ref_gpu_shape_ok.argtypes = [_c.c_int, _c.c_int]
         L.ref_gpu_fmha.argtypes = [_c.c_void_p, _c.POINTER(_c.c_float), _c.POINTER(_c.c_int)] + [_c.c_void_p] * 5
+        if hasattr(L, "wmma_layout_probe"):
+            L.wmma_layout_probe.argtypes = [_c.c_void_p, _c.c_void_p]
         _ref["gpu"] = L
     return _ref["gpu"]

@@ -1,6 +1,6 @@
 """CPU test of the benchmark's reference arm (`bench.py --impl reference`): it needs no GPU, runs the
 reference project's CPU path (or the oracle port when that library is absent) and must print one JSON line
-with the keys the round-end harness reads."""
+with the keys a harness that compares the two arms reads."""
 import json
 import os
 import subprocess
