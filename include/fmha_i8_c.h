@@ -10,8 +10,13 @@
  *             non-zero byte = key masked out (inc/cpuSoftmax.hpp:24, inc/fmha_i8.cuh:189-192)
  *   stream  : a cudaStream_t passed as void* (NULL = default stream)
  *   return  : FMHA_I8_OK or a negative FMHA_I8_ERR_* decided on the host before anything is
- *             launched.  Device-side trouble (a bounded wait that ran out) is reported through
- *             fmha_i8_sm100_device_status().
+ *             launched.  Device-side trouble (a bounded wait that ran out in a kernel launched
+ *             earlier) is reported in two ways: the details through fmha_i8_sm100_device_status(),
+ *             and -- for callers of the void C++ entry point, who never ask -- ONCE as
+ *             FMHA_I8_ERR_DEVICE by the first forward call made after the failing kernel has
+ *             finished; that call launches nothing, the next one runs again.  The kernels
+ *             themselves never look at the status words: one failure does not switch the
+ *             library off.
  * All device-pointer entry points enqueue on the stream and return without synchronising.
  */
 #ifndef FMHA_I8_C_H_
@@ -106,6 +111,15 @@ int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4],
                              const void* host_q, const void* host_k, const void* host_v,
                              const void* host_mask, void* host_o, unsigned flags);
 
+/* The same for heads [bh_begin, bh_begin + bh_count) of the flattened batch*head axis: host_q/k/v/o point at
+ * the FIRST head of the slice (each process holds only its slice), host_mask is the whole [B,S] mask and desc
+ * the whole shape.  This is what one rank of a multi-GPU job calls when its inputs live in host memory.  The
+ * reference has no counterpart (one GPU, grid = (batch, head), src/fmha_i8.cu:43). */
+int fmha_i8_sm100_infer_host_slice(const float amax[5], const int desc[4],
+                                   const void* host_q, const void* host_k, const void* host_v,
+                                   const void* host_mask, void* host_o, int bh_begin, int bh_count,
+                                   unsigned flags);
+
 /* Debug: S_int32[bh, i, j] = sum_d q[bh,i,d] k[bh,j,d] written as int32 [B*H, S, S] through the
  * same TMA + tensor-core stage the forward pass uses (GEMM 1, inc/fmha_i8.cuh:120-172).  For
  * bit-exact checks against cpuGEMM<int32_t,int32_t,int8_t,int32_t>; small shapes only. */
@@ -131,10 +145,10 @@ int fmha_i8_sm100_debug_simt_x(void* stream, const float amax[5], const int desc
 
 /* Debug: shows what a host sees when a device-side wait gives up, without faulting anything.  One warp
  * waits for at most limit_cycles (1000 ... 2e9 SM cycles) on a barrier that never completes, records
- * FMHA_I8_DEV_WAIT_DEBUG in the status words and returns normally; the context stays usable.  While the
- * status words are non-zero the forward kernel refuses to start (its CTAs return at once, o is not
- * written); fmha_i8_sm100_device_status() reports and clears them.  No counterpart in the reference,
- * which checks nothing. */
+ * FMHA_I8_DEV_WAIT_DEBUG in the status words and returns normally; the context stays usable.  The first
+ * forward call the host makes after that kernel has finished returns FMHA_I8_ERR_DEVICE once (nothing
+ * is launched); fmha_i8_sm100_device_status() reports the words and clears them.  No counterpart in the
+ * reference, which checks nothing. */
 int fmha_i8_sm100_debug_wait_probe(void* stream, long long limit_cycles);
 
 /* Per-tensor symmetric quantisation on the device, the producer step in front of the attention call:

@@ -32,6 +32,7 @@ FLAG_UINT8_P = 2     # P quantised as unsigned 8 bit, 255 levels (the reference 
 
 EXPORTS = (
     "fmha_i8_sm100_infer", "fmha_i8_sm100_infer_slice", "fmha_i8_sm100_infer_cross", "fmha_i8_sm100_calibrate_o_amax", "fmha_i8_sm100_infer_host",
+    "fmha_i8_sm100_infer_host_slice",
     "fmha_i8_sm100_debug_qk", "fmha_i8_sm100_debug_pv", "fmha_i8_sm100_debug_simt", "fmha_i8_sm100_debug_simt_x", "fmha_i8_sm100_debug_wait_probe",
     "fmha_i8_sm100_quantize_f32", "fmha_i8_sm100_quantize_f32_noalloc", "fmha_i8_sm100_device_status", "fmha_i8_sm100_last_status", "fmha_i8_sm100_status_string",
     "fmha_i8_sm100_launch_count", "fmha_i8_sm100_version",
@@ -99,6 +100,7 @@ def lib():
         L.fmha_i8_sm100_infer_cross.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, u]
         L.fmha_i8_sm100_calibrate_o_amax.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, u]
         L.fmha_i8_sm100_infer_host.argtypes = [fp, ip, vp, vp, vp, vp, vp, u]
+        L.fmha_i8_sm100_infer_host_slice.argtypes = [fp, ip, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, u]
         L.fmha_i8_sm100_debug_qk.argtypes = [vp, ip, vp, vp, vp]
         L.fmha_i8_sm100_debug_pv.argtypes = [vp, ip, vp, vp, vp, u]
         L.fmha_i8_sm100_debug_simt.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp]
@@ -199,6 +201,16 @@ def FMHAInferI8Host(fmha_param, attn_desc, host_q, host_k, host_v, host_mask, ho
                                         _ptr(host_mask), _ptr(host_o), _flags(True, uint8_p))
     if check and st != OK:
         raise FmhaError(st, "FMHAInferI8Host")
+    return st
+
+
+def FMHAInferI8HostSlice(fmha_param, attn_desc, host_q, host_k, host_v, host_mask, host_o, bh_begin, bh_count,
+                         check=True, uint8_p=False):
+    """Host buffers of heads [bh_begin, bh_begin+bh_count) in, host buffer of those heads out; the mask is whole."""
+    st = lib().fmha_i8_sm100_infer_host_slice(fmha_param.as_c(), attn_desc.as_c(), _ptr(host_q), _ptr(host_k), _ptr(host_v),
+                                              _ptr(host_mask), _ptr(host_o), int(bh_begin), int(bh_count), _flags(True, uint8_p))
+    if check and st != OK:
+        raise FmhaError(st, "FMHAInferI8HostSlice")
     return st
 
 

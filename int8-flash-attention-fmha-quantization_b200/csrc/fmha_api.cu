@@ -107,7 +107,6 @@ int set_kernel_attributes(DeviceInfo* d) {
   if (e != cudaSuccess) { cudaGetLastError(); return FMHA_I8_ERR_LAUNCH; }
   // The forward kernel redistributes registers with setmaxnreg; that only terminates if the launch
   // allocation is the one the targets were sized for.
-  static_assert(FwdRegs::kMerge <= 255, "register targets");
   cudaFuncAttributes fa64{}, fa128{};
   if (cudaFuncGetAttributes(&fa64, reinterpret_cast<const void*>(&fmha_fwd_kernel<64>)) != cudaSuccess ||
       cudaFuncGetAttributes(&fa128, reinterpret_cast<const void*>(&fmha_fwd_kernel<128>)) != cudaSuccess ||
@@ -351,14 +350,19 @@ int fmha_i8_sm100_calibrate_o_amax(void* stream, const float amax[5], const int 
   return finish(infer_x_impl(stream, a, sh, q, k, v, mask, nullptr, 0, static_cast<int>(BH), flags, o_amax_out));
 }
 
-int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void* host_q, const void* host_k,
-                             const void* host_v, const void* host_mask, void* host_o, unsigned flags) {
-  if (!amax || !desc || !host_q || !host_k || !host_v || !host_mask || !host_o) return finish(FMHA_I8_ERR_NULL_POINTER);
+// Host buffers in, host buffer out, for heads [bh_begin, bh_begin + bh_count): host_q/k/v/o point at the first head
+// of the slice, host_mask is the whole [B,S] mask.
+static int infer_host_slice_impl(const float amax[5], const int desc[4], const void* host_q, const void* host_k,
+                                 const void* host_v, const void* host_mask, void* host_o, int bh_begin, int bh_count, unsigned flags) {
+  if (!amax || !desc || !host_q || !host_k || !host_v || !host_mask || !host_o) return FMHA_I8_ERR_NULL_POINTER;
   int st = check_shape(desc);
-  if (st != FMHA_I8_OK) return finish(st);
+  if (st != FMHA_I8_OK) return st;
+  const long long BH_all = static_cast<long long>(desc[0]) * desc[2];
+  if (bh_begin < 0 || bh_count < 1 || static_cast<long long>(bh_begin) + bh_count > BH_all) return FMHA_I8_ERR_BAD_SLICE;
   int dev_id = 0;
-  if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= kMaxDevices) return finish(FMHA_I8_ERR_LAUNCH);
-  const size_t tensor_bytes = static_cast<size_t>(desc[0]) * desc[2] * desc[1] * desc[3];
+  if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= kMaxDevices) return FMHA_I8_ERR_LAUNCH;
+  const size_t head_bytes = static_cast<size_t>(desc[1]) * desc[3];
+  const size_t tensor_bytes = static_cast<size_t>(bh_count) * head_bytes;
   const size_t mask_bytes = static_cast<size_t>(desc[0]) * desc[1];
   std::lock_guard<std::mutex> lock(g_staging_mutex[dev_id]);
   HostStaging& s = g_staging[dev_id];
@@ -369,7 +373,7 @@ int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void*
     for (int i = 0; i < kHostChunks && good; ++i)
       good = cudaEventCreateWithFlags(&s.landed[i], cudaEventDisableTiming) == cudaSuccess &&
              cudaEventCreateWithFlags(&s.computed[i], cudaEventDisableTiming) == cudaSuccess;
-    if (!good) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
+    if (!good) { cudaGetLastError(); return FMHA_I8_ERR_LAUNCH; }
     s.ready = true;
   }
   if (s.tensor_cap < tensor_bytes) {
@@ -379,7 +383,7 @@ int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void*
     if (cudaMalloc(&s.q, tensor_bytes) != cudaSuccess || cudaMalloc(&s.k, tensor_bytes) != cudaSuccess ||
         cudaMalloc(&s.v, tensor_bytes) != cudaSuccess || cudaMalloc(&s.o, tensor_bytes) != cudaSuccess) {
       cudaGetLastError();
-      return finish(FMHA_I8_ERR_LAUNCH);
+      return FMHA_I8_ERR_LAUNCH;
     }
     s.tensor_cap = tensor_bytes;
   }
@@ -387,12 +391,12 @@ int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void*
     cudaFree(s.mask);
     s.mask = nullptr;
     s.mask_cap = 0;
-    if (cudaMalloc(&s.mask, mask_bytes) != cudaSuccess) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
+    if (cudaMalloc(&s.mask, mask_bytes) != cudaSuccess) { cudaGetLastError(); return FMHA_I8_ERR_LAUNCH; }
     s.mask_cap = mask_bytes;
   }
   // Pipeline over contiguous ranges of heads: while chunk i is computed, chunk i+1 is on its way in and
-  // chunk i-1 on its way out (the bus is full duplex).  Each chunk is one fmha_i8_sm100_infer_slice.
-  const int BH = desc[0] * desc[2];
+  // chunk i-1 on its way out (the bus is full duplex).  Each chunk is one forward launch on a sub-slice.
+  const int BH = bh_count;
   const int n_chunks = BH < kHostChunks ? BH : kHostChunks;
   // The inbound copies are the bottleneck, so what follows the last of them -- the last chunk's kernel and its
   // outbound copy -- is exposed: with enough heads the last chunk is made small (1/24 of the heads) and the
@@ -404,7 +408,6 @@ int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void*
     for (int i = 0; i <= n_body; ++i) bounds[i] = static_cast<int>(static_cast<long long>(body) * i / n_body);
     if (tail) bounds[n_chunks] = BH;
   }
-  const size_t head_bytes = static_cast<size_t>(desc[1]) * desc[3];
   cudaError_t e = cudaMemcpyAsync(s.mask, host_mask, mask_bytes, cudaMemcpyHostToDevice, s.s_in);
   for (int i = 0; i < n_chunks && e == cudaSuccess; ++i) {
     const int begin = bounds[i];
@@ -423,7 +426,7 @@ int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void*
     if (e == cudaSuccess) e = cudaEventRecord(s.landed[i], s.s_in);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(s.s_run, s.landed[i], 0);
     if (e != cudaSuccess) break;
-    st = infer_slice_impl(s.s_run, amax, desc, dq, dk, dv, s.mask, dout, begin, end - begin, flags);
+    st = infer_slice_impl(s.s_run, amax, desc, dq, dk, dv, s.mask, dout, bh_begin + begin, end - begin, flags);
     if (st != FMHA_I8_OK) break;
     e = cudaEventRecord(s.computed[i], s.s_run);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(s.s_out, s.computed[i], 0);
@@ -431,9 +434,23 @@ int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void*
   }
   // drain all three streams whatever happened, so the staging buffers are idle when the lock is released
   const cudaError_t e1 = cudaStreamSynchronize(s.s_in), e2 = cudaStreamSynchronize(s.s_run), e3 = cudaStreamSynchronize(s.s_out);
-  if (st != FMHA_I8_OK) return finish(st);
-  if (e != cudaSuccess || e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess) { cudaGetLastError(); return finish(FMHA_I8_ERR_LAUNCH); }
-  return finish(FMHA_I8_OK);
+  if (st != FMHA_I8_OK) return st;
+  if (e != cudaSuccess || e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess) { cudaGetLastError(); return FMHA_I8_ERR_LAUNCH; }
+  return FMHA_I8_OK;
+}
+
+int fmha_i8_sm100_infer_host(const float amax[5], const int desc[4], const void* host_q, const void* host_k,
+                             const void* host_v, const void* host_mask, void* host_o, unsigned flags) {
+  if (!desc) return finish(FMHA_I8_ERR_NULL_POINTER);
+  const long long BH = static_cast<long long>(desc[0]) * desc[2];
+  if (BH < 1 || BH > 0x7FFFFFFFLL) return finish(FMHA_I8_ERR_BAD_SHAPE);
+  return finish(infer_host_slice_impl(amax, desc, host_q, host_k, host_v, host_mask, host_o, 0, static_cast<int>(BH), flags));
+}
+
+int fmha_i8_sm100_infer_host_slice(const float amax[5], const int desc[4], const void* host_q, const void* host_k,
+                                   const void* host_v, const void* host_mask, void* host_o, int bh_begin, int bh_count,
+                                   unsigned flags) {
+  return finish(infer_host_slice_impl(amax, desc, host_q, host_k, host_v, host_mask, host_o, bh_begin, bh_count, flags));
 }
 
 int fmha_i8_sm100_debug_qk(void* stream, const int desc[4], const void* q, const void* k, int32_t* s_out) {

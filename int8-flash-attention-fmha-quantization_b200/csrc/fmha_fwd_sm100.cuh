@@ -10,43 +10,44 @@
 //                phases, the K/V ring and tensor memory carry on from one unit to the next, so no role
 //                drains at a unit boundary.
 //   two chains = the softmax warps form two teams; steps alternate between them (chain = g & 1).
-//   three S     = S = Q.K^T of step g lands in accumulator g % 3 of tensor memory, so S(g+2), the next
-//   buffers       step of the team that is working on step g, has been computed before that team needs
-//                 it: the softmax warps never wait for the tensor core in steady state.
+//   S buffers  = S = Q.K^T of step g lands in accumulator g % n of tensor memory (n = 3 at head_dim 128, 4 at
+//                head_dim 64), issued as soon as that accumulator is free, i.e. several steps ahead of the
+//                softmax warps.  The same accumulator then carries the step through the rest of its life: the
+//                softmax threads overwrite the two ends of it with the 8-bit P row, and P.V of the step writes
+//                its partial output into the 96 columns in between (head_dim 128: 96 columns there and the last
+//                32 in a small annex).  So every step in flight owns its whole set of buffers and no role ever
+//                waits for another STEP's buffer, only for its own step's previous stage.
 //
-//   warps 0-15   softmax: warps 0-7 serve chain 0, warps 8-15 chain 1.  TWO threads share one query
-//                row: thread `half` owns keys [64*half, 64*half+64) of the tile.  Each reads its part
-//                of S twice (integer max, then exp + requantise), the two exchange their maxima
-//                through shared memory, and each writes its 8-bit P values over the front of the S
-//                columns it has just consumed.  Four warps per SM sub-partition keep the exp unit fed;
-//                these threads hold no output row, so they are light (64 registers).
-//   warps 16-23  merge: two threads per query row, each holding one half (D/2 columns) of the fp32
-//                running output row.  P.V of a step is computed in two halves of D/2 columns into two
-//                small accumulators; after each half the merge thread of that half drains it from
-//                tensor memory, rescales and adds it, while the tensor core works on the other half.
-//                At the end of a unit the merge threads normalise, requantise and store the row.
-//   warp 24      K loader: TMA brings Q (once per unit, double-buffered) and a ring of K tiles into
+//   warp 0       loader: TMA brings Q (once per unit, in a small ring) and rings of K and of V tiles into
 //                swizzled shared memory, running ahead into the next units.
-//   warp 25      MMA issuer: one thread issues tcgen05.mma
-//                  S_b    = bias + Q . K_g^T          (smem x smem -> int32 in tensor memory), b = g % 3
-//                  O~_h   = P_b . V_g[:, half h]      (tmem x smem -> int32 in tensor memory), h = 0, 1
-//                in the order  ... P.V(g), S(g+3), P.V(g+1), S(g+4) ...
-//   warp 26      scanner: turns the coming units' padding-mask rows into per-tile bit masks and the
-//                list of key tiles that hold at least one unmasked key (ring of four).
-//   warp 27      V loader: a ring of V tiles (kept apart from K: a K tile is needed three steps
-//                earlier than the V tile of the same step and is released much sooner).
+//   warp 1       S issuer:  S_b = bias + Q . K_g^T  (tcgen05.mma smem x smem -> int32 in tensor memory).
+//   warp 2       scanner: turns the coming units' padding-mask rows into per-tile bit masks and the list of
+//                key tiles that hold at least one unmasked key (ring of four).
+//   warp 3       P.V issuer:  O~ = bias + P_b . V_g  (tcgen05.mma tmem x smem -> int32 in tensor memory) when the
+//                softmax warps have written P_b.
+//                These four run warp-wide -- every lane waits and counts, one elected lane issues -- so that
+//                descriptors and addresses are warp-uniform values; issued from a single divergent lane an MMA
+//                cost about 100 cycles of issue time, this way about 70.
+//   warps 4-11   merge: two threads per query row, each holding one half (D/2 columns) of the fp32 running
+//                output row.  After P.V of a step they drain the partial output from tensor memory, rescale
+//                and add it; at the end of a unit they normalise, requantise and store the row.  This keeps
+//                the per-tile drain and the epilogue off the softmax warps.
+//   warps 12-27  softmax: warps 12-19 serve chain 0, warps 20-27 chain 1.  TWO threads share one query row:
+//                thread `half` owns keys [64*half, 64*half+64) of the tile.  Each reads its part of S twice
+//                (integer max, then exp + requantise), the two exchange their maxima through shared memory,
+//                and each writes its 8-bit P values over columns it has already consumed (the lower half row
+//                walks up and leaves P in columns [0,16), the upper one walks down and leaves it in [112,128)).
+//                These threads hold no output row, so they are light (64 registers).
 //
-// The bias: the S accumulator is first written by a one-step fp16 MMA whose operands hold 4096 and
+// The bias: every accumulator is first written by a one-step fp16 MMA whose operands hold 4096 and
 // 3072, i.e. the fp32 value 1.5*2^23 (bits 0x4B400000); the int8 MMAs then add their integer result
-// to that bit pattern.  Read back as a float the accumulator is exactly 1.5*2^23 + s, so the softmax
-// threads never convert integers to floats: one fused multiply-add turns the raw accumulator into the
-// exponent argument.  The merge threads get the same effect with one integer addition of 0x4B400000
-// per element of the partial output.
+// to that bit pattern.  Read back as a float the accumulator is exactly 1.5*2^23 + s, so no thread
+// ever converts integers to floats: one fused multiply-add turns the raw accumulator into the
+// exponent argument (or into the rescaled partial output).
 //
-// Tensor memory (512 columns x 128 lanes x 32 bit): S_0 [0,128) S_1 [128,256) S_2 [256,384)
-// O~_lo [384,384+D/2) O~_hi [384+D/2,384+D).  P of a step: keys 0-63 in columns [0,16) of its S
-// buffer, keys 64-127 in columns [64,80) (four int8 per column), each written by the thread that
-// consumed those S columns.
+// Tensor memory (512 columns x 128 lanes x 32 bit): accumulator b at columns [128 b, 128 b + 128); at head_dim
+// 128 annex b at [384 + 32 b, 384 + 32 b + 32).  Inside an accumulator, after the softmax: P of keys 0-63 in
+// columns [0,16), P of keys 64-127 in columns [112,128) (four int8 per column), partial output in [16, 16+min(D,96)).
 //
 // Numerics kept equal to the reference kernel within the test tolerance: the running output is kept
 // unnormalised (divided by the row sum once at the end) instead of renormalised after every tile,
@@ -60,18 +61,24 @@
 #include "ptx.cuh"
 #include "../../include/fmha_i8_c.h"
 
+// 1: the partial-output accumulators are preset to the bit pattern of 1.5*2^23 by a one-step fp16 MMA (as the S
+//    accumulators are), so the merge threads read floats; 0: they add that bit pattern themselves, one integer
+//    addition per element.
+#ifndef FMHA_PV_BIAS_MMA
+#define FMHA_PV_BIAS_MMA 1
+#endif
 // Ring depths can be overridden at compile time for tuning runs.
 #ifndef FMHA_STAGES_K128
 #define FMHA_STAGES_K128 3
 #endif
 #ifndef FMHA_STAGES_V128
-#define FMHA_STAGES_V128 4
+#define FMHA_STAGES_V128 6
 #endif
 #ifndef FMHA_STAGES_K64
 #define FMHA_STAGES_K64 4
 #endif
 #ifndef FMHA_STAGES_V64
-#define FMHA_STAGES_V64 6
+#define FMHA_STAGES_V64 8
 #endif
 
 namespace fmha {
@@ -93,26 +100,38 @@ constexpr int kSoftmaxWarps = 16;    // 2 chains x 2 key halves x 4 lane quarter
 constexpr int kMergeWarps = 8;       // 2 column halves x 4 lane quarters
 constexpr int kFwdWarps = kSoftmaxWarps + kMergeWarps + 4;
 constexpr int kFwdThreads = kFwdWarps * 32;          // 896
-constexpr int kWarpMerge0 = kSoftmaxWarps;
-constexpr int kWarpLoadK = kSoftmaxWarps + kMergeWarps;
-constexpr int kWarpMma = kWarpLoadK + 1;
-constexpr int kWarpScan = kWarpLoadK + 2;
-constexpr int kWarpLoadV = kWarpLoadK + 3;
-constexpr int kSBufs = 3;            // S accumulators in tensor memory
+// Warp numbering: the one-warp roles first, then the merge warps, then the softmax warps (a role's lane quarter of
+// tensor memory is its warp number modulo 4; register targets are set per group of four warps).
+constexpr int kWarpLoad = 0;
+constexpr int kWarpMmaS = 1;
+constexpr int kWarpScan = 2;
+constexpr int kWarpMmaO = 3;
+constexpr int kWarpMerge0 = 4;
+constexpr int kWarpSoftmax0 = kWarpMerge0 + kMergeWarps;
+constexpr int kSBufsMax = 4;
+// S accumulators in tensor memory: three of 128 columns plus three 32-column annexes at head_dim 128 (480 columns),
+// four at head_dim 64, where the partial output fits between the P bytes of its own accumulator (512 columns)
+template <int D> struct SBufs { static constexpr int n = (D == 128) ? 3 : 4; };
+constexpr int kOOff = 16;            // the partial output of a step starts at this column of the step's S accumulator ...
+constexpr int kOMain = 96;           // ... and may use this many columns there (between the two blocks of P bytes);
+constexpr int kOAnnex = 32;          // head_dim 128 puts its last 32 output columns into an annex of that accumulator
 constexpr int kInfoBufs = 4;         // units whose mask information is resident at once
-constexpr int kInfoConsumers = 3 + kSoftmaxWarps + kMergeWarps;   // two loaders, issuer, softmax and merge warps release an info buffer once each
+constexpr int kInfoConsumers = 3 + kSoftmaxWarps + kMergeWarps;   // loader, two issuers, softmax and merge warps release an info buffer once each
 // setmaxnreg moves registers inside the CTA's own launch allocation (registers per thread at launch x
 // threads), not inside the SM's whole register file: a request that does not fit blocks forever.  With
 // 896 threads the launch allocation is 72 registers per thread (the host checks this before the first
-// launch and refuses otherwise): 16 x 64 (softmax) + 8 x 96 (merge: a 64-register half output row)
-// + 4 x 56 (loaders, issuer, scanner) = 28 x 72.
+// launch and refuses otherwise); the targets per role (FwdRegs) add up to 28 x 72.
 constexpr int kLaunchRegs = 72;
-struct FwdRegs {
-  static constexpr int kSoftmax = 64, kMerge = 96, kOther = 56;
+template <int D> struct FwdRegs {
+  // head_dim 128: the merge threads hold a 64-register half output row, the single-thread roles run lean
+  // (measured on C3: 104/40 is 2 % faster than 96/56); head_dim 64: the output row is 32 registers and the
+  // single-thread roles, which sit on every unit boundary of the short-sequence shapes, get the rest.
+  static constexpr int kSoftmax = 64, kMerge = (D == 128) ? 104 : 80, kOther = (D == 128) ? 40 : 88;
   static_assert(kSoftmaxWarps * kSoftmax + kMergeWarps * kMerge + 4 * kOther <= kFwdWarps * kLaunchRegs,
                 "setmaxnreg targets exceed the CTA's register allocation: the kernel would hang");
-  static_assert(kSoftmax <= kLaunchRegs && kOther <= kLaunchRegs && kMerge >= kLaunchRegs, "only the merge warps gain registers");
+  static_assert(kSoftmax <= kLaunchRegs && kMerge >= kLaunchRegs, "the softmax warps give registers, the merge warps gain");
 };
+
 constexpr uint32_t kTmemCols = 512;
 constexpr float kMagic = 12582912.0f;          // 1.5 * 2^23: float whose ulp is 1 over [2^23, 2^24)
 constexpr uint32_t kMagicBits = 0x4B400000u;
@@ -121,7 +140,10 @@ constexpr int kBiasBytes = 4096;               // 128 rows x 16 fp16, unswizzled
 template <int D> struct FwdCfg {
   static_assert(D == 64 || D == 128, "head_dim must be 64 or 128");
   static constexpr int kStagesK = (D == 128) ? FMHA_STAGES_K128 : FMHA_STAGES_K64;   // ring depth of K
-  static constexpr int kStagesV = (D == 128) ? FMHA_STAGES_V128 : FMHA_STAGES_V64;   // ring depth of V
+  // ring depth of V: one thread loads K(g), V(g), K(g+1), ... in order, and V(g) is consumed a few steps (the number of S accumulators) after
+  // K(g), so the V ring has to be that much deeper than the K ring
+  static constexpr int kStagesV = (D == 128) ? FMHA_STAGES_V128 : FMHA_STAGES_V64;
+  static_assert(kStagesV >= kStagesK + SBufs<D>::n, "V ring too shallow for the in-order loader");
   // Q tiles resident at once: the S cursor runs three steps ahead, which with one-tile units means three
   // units ahead, so short-sequence shapes want more than two (head_dim 128 has no shared memory to spare)
   static constexpr int kQBufs = (D == 128) ? 2 : 4;
@@ -162,8 +184,9 @@ struct UnitInfo {
 template <int NK, int NV> struct FwdCtl {
   uint64_t q_full[4], q_empty[4];      // Q ring (kQBufs used): rows have landed / the unit's last S = Q.K^T has completed
   uint64_t k_full[NK], k_empty[NK], v_full[NV], v_empty[NV];
-  uint64_t s_full[kSBufs];             // per S accumulator
-  uint64_t o_full[2], o_free[2];       // per half of the partial output (columns [0,D/2) and [D/2,D))
+  uint64_t s_full[kSBufsMax];          // per S accumulator: S = Q.K^T has completed
+  uint64_t s_free[kSBufsMax];          // per S accumulator: the merge threads have drained the partial output that lived in it
+  uint64_t o_full[kSBufsMax];          // per S accumulator: P.V of the step that owns it has completed
   uint64_t p_ready[4];                 // per step slot (g & 3): P written, row statistics published
   uint64_t xch[2][4];                  // per chain and lane quarter: the two half-row threads have published their maxima
   uint64_t info_full[kInfoBufs], info_empty[kInfoBufs];
@@ -328,13 +351,18 @@ __device__ __forceinline__ RowConsts row_consts(const int imax, const float c2s,
   return k;
 }
 
-// o2 (+)= e_cur * (P8 . V) for N output columns.  r = raw int32 accumulator (|r| < 2^22); adding the bit
-// pattern of 1.5*2^23 makes it the float kMagic + r without a conversion instruction.
+// o2 (+)= e_cur * (P8 . V) for N output columns.  r = accumulator: either preset by the bias MMA, so that it reads
+// as the float kMagic + (P8 . V), or a raw int32 (|r| < 2^22) that becomes that float by adding the bit pattern
+// of 1.5*2^23 -- no conversion instruction either way.
 template <int N>
 __device__ __forceinline__ void drain_chunk(const uint32_t (&r)[N], float2* o2, const float2 neg_ec, const float2 e_bias, const float2 e_old) {
 #pragma unroll
   for (int i = 0; i < N / 2; ++i) {
+#if FMHA_PV_BIAS_MMA
+    const float2 x = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+#else
     const float2 x = make_float2(__uint_as_float(r[2 * i] + kMagicBits), __uint_as_float(r[2 * i + 1] + kMagicBits));
+#endif
     const float2 t = __ffma2_rn(x, neg_ec, e_bias);          // e_cur * (P8 . V), exact product before rounding
     o2[i] = __ffma2_rn(o2[i], e_old, t);
   }
@@ -358,7 +386,7 @@ __device__ __forceinline__ UnitGeom unit_geom(const FwdParams& p, int u) {
 template <int D>
 __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D>::kStagesK, FwdCfg<D>::kStagesV>* ctl, const uint32_t tmem_base,
                                              const int first_unit, const int unit_step) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = (threadIdx.x >> 5) - kWarpSoftmax0, lane = threadIdx.x & 31;
   const int chain = warp >> 3, half = (warp >> 2) & 1, quad = warp & 3;
   const int row = quad * 32 + lane;
   // my 64 columns of S buffer 0; my P bytes go over their first 16 columns
@@ -372,7 +400,7 @@ __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D
   int it = 0;
   for (int u = first_unit; u < p.n_units; u += unit_step, ++it) {
     const int buf = it % kInfoBufs;
-    if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it / kInfoBufs) & 1), abort_flag))) {
+    if (!__all_sync(0xFFFFFFFFu, mbar_wait_slow(smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it / kInfoBufs) & 1), abort_flag))) {
       raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_INFO, it);
       return;
     }
@@ -381,32 +409,36 @@ __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D
 #pragma unroll 1
     for (int j = (chain ^ static_cast<int>(g0)) & 1; j < n_live; j += 2, ++n) {
       const uint32_t g = g0 + static_cast<uint32_t>(j);
-      const uint32_t sb = g % kSBufs;                       // S accumulator of this step
+      const uint32_t sb = g % SBufs<D>::n;                       // S accumulator of this step
       const uint32_t tS = tS0 + sb * kTile;
-      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&ctl->s_full[sb]), (g / kSBufs) & 1u, abort_flag))) {
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&ctl->s_full[sb]), (g / SBufs<D>::n) & 1u, abort_flag))) {
         raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_S_READY, g);
         return;
       }
       tc_fence_after();
       if (half == 0 && quad == 0) FMHA_STAMP(chain * 4 + 0, n);
-      FMHA_STAMP(32 + warp, n);
       const bool mixed = info->mixed[j] != 0;
       // the 64 mask bits of my keys (only looked at on the mixed path)
       const uint32_t* mwords = &info->maskbits[4 * info->live[j] + 2 * half];
+
+      // Order of my four 16-column chunks: the lower half row walks up and leaves its P bytes in the first 16 of its
+      // 64 columns, the upper half row walks DOWN and leaves them in the last 16, always over columns it has already
+      // consumed.  What stays untouched in between, columns [16,112) of the accumulator, is where P.V of this step
+      // will put the partial output.
+      const int c0 = half ? 3 : 0, cs = half ? -1 : 1;                 // first chunk and direction
+      const uint32_t tP = tS + (half ? 48u : 0u);                      // my 16 columns of P
 
       // ---- pass 1: biased integer maximum of my 64 columns (inc/fmha_i8.cuh:183-206)
       int max_a = INT_MIN, max_b = INT_MIN;
       uint32_t ra[16], rb[16];
       if (!mixed) {
-        tmem_ld16_issue(tS, ra);
-        tmem_ld_fence(ra); tmem_ld16_issue(tS + 16, rb);
-        chunk_max<false, 16>(ra, 0u, max_a, max_b);
-        tmem_ld_fence(rb); tmem_ld16_issue(tS + 32, ra);
-        chunk_max<false, 16>(rb, 0u, max_a, max_b);
-        tmem_ld_fence(ra); tmem_ld16_issue(tS + 48, rb);
-        chunk_max<false, 16>(ra, 0u, max_a, max_b);
-        tmem_ld_fence(rb); tmem_ld16_issue(tS, ra);           // first chunk of pass 2, in flight during the exchange
-        chunk_max<false, 16>(rb, 0u, max_a, max_b);
+        // two tensor-memory round trips (a round trip costs about as much as the whole arithmetic of this pass)
+        uint32_t wide[32];
+        tmem_ld32(tS, wide);
+        chunk_max<false, 32>(wide, 0u, max_a, max_b);
+        tmem_ld32(tS + 32, wide);
+        tmem_ld16_issue(tS + c0 * 16, ra);                             // first chunk of pass 2, in flight during the exchange
+        chunk_max<false, 32>(wide, 0u, max_a, max_b);
       } else {
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -414,7 +446,7 @@ __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D
           tmem_ld_fence(ra);
           chunk_max<true, 16>(ra, (mwords[c >> 1] >> ((c & 1) * 16)) & 0xFFFFu, max_a, max_b);
         }
-        tmem_ld16_issue(tS, ra);
+        tmem_ld16_issue(tS + c0 * 16, ra);
       }
       const int mine = max(max_a, max_b);
       // ---- exchange with the thread that owns the other half of this row
@@ -430,25 +462,26 @@ __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D
       const RowConsts k = row_consts(imax, c2s, row_scale, scale_qk, p_mul);
       if (half == 0 && quad == 0) FMHA_STAMP(chain * 4 + 1, n);
 
-      // ---- pass 2: exp, row sum, requantise, P over the front of my S columns (inc/fmha_i8.cuh:208-253)
+      // ---- pass 2: exp, row sum, requantise, P over columns already consumed (inc/fmha_i8.cuh:208-253)
       float2 sum[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       uint32_t packed[4];
       if (!mixed) {
-        tmem_ld_fence(ra); tmem_ld16_issue(tS + 16, rb);
-        chunk_exp_pack<false, 16>(ra, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed); tmem_st4(tS, packed);
-        tmem_ld_fence(rb); tmem_ld16_issue(tS + 32, ra);
-        chunk_exp_pack<false, 16>(rb, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed); tmem_st4(tS + 4, packed);
-        tmem_ld_fence(ra); tmem_ld16_issue(tS + 48, rb);
-        chunk_exp_pack<false, 16>(ra, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed); tmem_st4(tS + 8, packed);
+        tmem_ld_fence(ra); tmem_ld16_issue(tS + (c0 + cs) * 16, rb);
+        chunk_exp_pack<false, 16>(ra, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed); tmem_st4(tP + c0 * 4, packed);
+        tmem_ld_fence(rb); tmem_ld16_issue(tS + (c0 + 2 * cs) * 16, ra);
+        chunk_exp_pack<false, 16>(rb, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed); tmem_st4(tP + (c0 + cs) * 4, packed);
+        tmem_ld_fence(ra); tmem_ld16_issue(tS + (c0 + 3 * cs) * 16, rb);
+        chunk_exp_pack<false, 16>(ra, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed); tmem_st4(tP + (c0 + 2 * cs) * 4, packed);
         tmem_ld_fence(rb);
-        chunk_exp_pack<false, 16>(rb, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed); tmem_st4(tS + 12, packed);
+        chunk_exp_pack<false, 16>(rb, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed); tmem_st4(tP + (c0 + 3 * cs) * 4, packed);
       } else {
         tmem_ld_fence(ra);
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          if (c > 0) { tmem_ld16_issue(tS + c * 16, ra); tmem_ld_fence(ra); }
+        for (int i = 0; i < 4; ++i) {
+          const int c = c0 + i * cs;
+          if (i > 0) { tmem_ld16_issue(tS + c * 16, ra); tmem_ld_fence(ra); }
           chunk_exp_pack<true, 16>(ra, (mwords[c >> 1] >> ((c & 1) * 16)) & 0xFFFFu, k.c2, k.neg_hi, k.p_mul_f, sum, packed);
-          tmem_st4(tS + c * 4, packed);
+          tmem_st4(tP + c * 4, packed);
         }
       }
       // ---- publish the row statistics of this step for the merge threads
@@ -483,15 +516,14 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quad = warp & 3, ch = (warp - kWarpMerge0) >> 2;       // ch = which half of the output columns
   const int row = quad * 32 + lane;
-  const uint32_t tO = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(kSBufs * kTile + ch * DH);
-  const uint32_t bar_full = smem_u32(&ctl->o_full[ch]), bar_free = smem_u32(&ctl->o_free[ch]);
+  const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
   volatile int* abort_flag = &ctl->abort;
 
   uint32_t g0 = 0;
   int it = 0;
   for (int u = first_unit; u < p.n_units; u += unit_step, ++it) {
     const int buf = it % kInfoBufs;
-    if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it / kInfoBufs) & 1), abort_flag))) {
+    if (!__all_sync(0xFFFFFFFFu, mbar_wait_slow(smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it / kInfoBufs) & 1), abort_flag))) {
       raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_INFO, it);
       return;
     }
@@ -510,7 +542,8 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
     for (int j = 0; j < n_live; ++j) {
       const uint32_t g = g0 + static_cast<uint32_t>(j);
       const int slot = static_cast<int>(g & 3u);
-      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&ctl->p_ready[slot]), (g >> 2) & 1u, abort_flag))) {
+      const uint32_t sb = g % SBufs<D>::n;
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait_slow(smem_u32(&ctl->p_ready[slot]), (g >> 2) & 1u, abort_flag))) {
         raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_P_READY, g);
         return;
       }
@@ -526,27 +559,36 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
       const float2 neg_ec = make_float2(es, es), e_bias = make_float2(-es * kMagic, -es * kMagic);
       const float2 e_old2 = make_float2(e_old, e_old);
 
-      // ---- drain my half of O~ = -/+ (P8 . V) into the fp32 running row
-      if (!__all_sync(0xFFFFFFFFu, mbar_wait(bar_full, g & 1u, abort_flag))) {
+      // ---- drain my half of O~ = bias -/+ (P8 . V) into the fp32 running row.  The partial output of step g lives in
+      //      the accumulator S(g) came from: columns [16, 16 + min(D, 96)) of it, and for head_dim 128 the last 32
+      //      output columns in a 32-column annex of that accumulator.
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&ctl->o_full[sb]), (g / SBufs<D>::n) & 1u, abort_flag))) {
         raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_O_READY, g);
         return;
       }
       tc_fence_after();
       if (quad == 0) FMHA_STAMP(8 + 2 * ch, g);
       {
-        // 16-column chunks, the next load in flight while the current chunk is folded in
+        // output column c of this step: tensor-memory column of 16-column chunk i of MY half
+        auto chunk_col = [&](int i) -> uint32_t {
+          const int c = ch * DH + i * 16;                                   // output column
+          return (c < kOMain) ? (t_lane + sb * kTile + kOOff + c) : (t_lane + SBufs<D>::n * kTile + sb * kOAnnex + (c - kOMain));
+        };
+        // two loads in flight at a time: a round trip to tensor memory costs more than folding a chunk in
         uint32_t ra[16], rb[16];
-        tmem_ld16_issue(tO, ra);
+        tmem_ld16_issue(chunk_col(0), ra);
+        tmem_ld16_issue(chunk_col(1), rb);
 #pragma unroll
         for (int c = 0; c < DH / 16; c += 2) {
-          tmem_ld_fence(ra); tmem_ld16_issue(tO + (c + 1) * 16, rb);
+          tmem_ld_fence(ra); tmem_ld_fence(rb);
           drain_chunk<16>(ra, o2 + c * 8, neg_ec, e_bias, e_old2);
-          tmem_ld_fence(rb); if (c + 2 < DH / 16) tmem_ld16_issue(tO + (c + 2) * 16, ra);
+          if (c + 2 < DH / 16) tmem_ld16_issue(chunk_col(c + 2), ra);
           drain_chunk<16>(rb, o2 + (c + 1) * 8, neg_ec, e_bias, e_old2);
+          if (c + 3 < DH / 16) tmem_ld16_issue(chunk_col(c + 3), rb);
         }
       }
       tc_fence_before();
-      mbar_arrive(bar_free);
+      mbar_arrive(smem_u32(&ctl->s_free[sb]));
       if (quad == 0) FMHA_STAMP(9 + 2 * ch, g);
     }
     g0 += static_cast<uint32_t>(n_live);
@@ -593,59 +635,195 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
   }
 }
 
-// ---------------------------------------------------------------------------------------------- loaders
-// One thread each.  kLoadK: the Q tile of every non-empty unit and the ring of K tiles; otherwise the ring of V tiles.
-template <int D, bool kLoadK>
+// ---------------------------------------------------------------------------------------------- loader
+// One warp, run warp-wide (every lane waits and counts, one elected lane issues the copies): the Q tile of every
+// non-empty unit, then per step the K tile and the V tile, in step order.
+template <int D>
 __device__ __forceinline__ void loader_role(const FwdParams& p, FwdCtl<FwdCfg<D>::kStagesK, FwdCfg<D>::kStagesV>* ctl,
-                                            const CUtensorMap* map_q, const CUtensorMap* map_kv, const uint32_t q_smem, const uint32_t ring_smem,
+                                            const CUtensorMap* map_q, const CUtensorMap* map_k, const CUtensorMap* map_v,
+                                            const uint32_t q_smem, const uint32_t k_smem, const uint32_t v_smem,
                                             const int first_unit, const int unit_step) {
   using Cfg = FwdCfg<D>;
-  constexpr uint32_t NR = kLoadK ? Cfg::kStagesK : Cfg::kStagesV;
+  constexpr uint32_t NK = Cfg::kStagesK, NV = Cfg::kStagesV, NQ = Cfg::kQBufs;
   volatile int* abort_flag = &ctl->abort;
-  uint64_t* full = kLoadK ? ctl->k_full : ctl->v_full;
-  uint64_t* empty = kLoadK ? ctl->k_empty : ctl->v_empty;
   uint32_t g = 0;            // steps loaded so far: ring position and phase continue across units
   uint32_t qn = 0;           // non-empty units so far: Q buffer and phase
-  bool ok = true;
+  uint32_t fail = 0u, fail_tile = 0u;
   int it = 0;
-  for (int u = first_unit; u < p.n_units && ok; u += unit_step, ++it) {
+  for (int u = first_unit; u < p.n_units && fail == 0u; u += unit_step, ++it) {
     const int buf = it % kInfoBufs;
-    if (!mbar_wait(smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it / kInfoBufs) & 1), abort_flag)) {
-      raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_INFO, it); ok = false; break;
+    if (!__all_sync(0xFFFFFFFFu, mbar_wait_slow(smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it / kInfoBufs) & 1), abort_flag))) {
+      fail = FMHA_I8_DEV_WAIT_INFO; fail_tile = it; break;
     }
     const UnitGeom geo = unit_geom(p, u);
     const UnitInfo* info = &ctl->info[buf];
     const int n_live = info->n_live;
     if (n_live > 0) {
-      if (kLoadK) {
-        constexpr uint32_t NQ = Cfg::kQBufs;
-        const uint32_t qb = qn % NQ;
-        // the Q buffer is free once the last S = Q.K^T of the unit that used it NQ units ago has completed
-        if (qn >= NQ && !mbar_wait(smem_u32(&ctl->q_empty[qb]), ((qn / NQ) - 1) & 1u, abort_flag)) {
-          raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_K_FREE, it); ok = false; break;
-        }
+      const uint32_t qb = qn % NQ;
+      // the Q buffer is free once the last S = Q.K^T of the unit that used it NQ units ago has completed
+      if (qn >= NQ && !__all_sync(0xFFFFFFFFu, mbar_wait_slow(smem_u32(&ctl->q_empty[qb]), ((qn / NQ) - 1) & 1u, abort_flag))) {
+        fail = FMHA_I8_DEV_WAIT_K_FREE; fail_tile = it; break;
+      }
+      if (elect_one()) {
         const uint32_t bar_q = smem_u32(&ctl->q_full[qb]);
         mbar_arrive_expect_tx(bar_q, static_cast<uint32_t>(Cfg::kTileBytes));
         tma_load_3d(q_smem + qb * Cfg::kTileBytes, map_q, bar_q, 0, geo.q_row0, geo.bh_local);
-        ++qn;
       }
+      ++qn;
       for (int j = 0; j < n_live; ++j, ++g) {
         const int t = info->live[j];
-        const uint32_t s = g % NR, round = g / NR;
-        if (round > 0 && !mbar_wait(smem_u32(&empty[s]), (round - 1) & 1u, abort_flag)) {
-          raise_status(abort_flag, p.status, kLoadK ? FMHA_I8_DEV_WAIT_K_FREE : FMHA_I8_DEV_WAIT_V_FREE, g); ok = false; break;
+        const uint32_t sk = g % NK, rk = g / NK, sv = g % NV, rv = g / NV;
+        if (rk > 0 && !__all_sync(0xFFFFFFFFu, mbar_wait_slow(smem_u32(&ctl->k_empty[sk]), (rk - 1) & 1u, abort_flag))) {
+          fail = FMHA_I8_DEV_WAIT_K_FREE; fail_tile = g; break;
         }
-        mbar_arrive_expect_tx(smem_u32(&full[s]), Cfg::kTileBytes);
-        tma_load_3d(ring_smem + s * Cfg::kTileBytes, map_kv, smem_u32(&full[s]), 0, t * kTile, geo.bh_local);
+        if (elect_one()) {
+          mbar_arrive_expect_tx(smem_u32(&ctl->k_full[sk]), Cfg::kTileBytes);
+          tma_load_3d(k_smem + sk * Cfg::kTileBytes, map_k, smem_u32(&ctl->k_full[sk]), 0, t * kTile, geo.bh_local);
+        }
+        if (rv > 0 && !__all_sync(0xFFFFFFFFu, mbar_wait_slow(smem_u32(&ctl->v_empty[sv]), (rv - 1) & 1u, abort_flag))) {
+          fail = FMHA_I8_DEV_WAIT_V_FREE; fail_tile = g; break;
+        }
+        if (elect_one()) {
+          mbar_arrive_expect_tx(smem_u32(&ctl->v_full[sv]), Cfg::kTileBytes);
+          tma_load_3d(v_smem + sv * Cfg::kTileBytes, map_v, smem_u32(&ctl->v_full[sv]), 0, t * kTile, geo.bh_local);
+        }
       }
     }
-    mbar_arrive(smem_u32(&ctl->info_empty[buf]));
+    __syncwarp();
+    if (fail == 0u && elect_one()) mbar_arrive(smem_u32(&ctl->info_empty[buf]));
   }
-  if (!ok) {
+  if (fail != 0u) {
+    if (elect_one()) raise_status(abort_flag, p.status, fail, fail_tile);
     // unwinding: let copies that are still in flight land before the CTA may exit
     const long long t0 = clock64();
     while (clock64() - t0 < 2000000LL) { /* about a millisecond */ }
   }
+}
+
+// ---------------------------------------------------------------------------------------------- MMA issuers
+// Two warps issue tcgen05.mma: one the S = Q.K^T products, the other the P.V products.  Each runs warp-wide (every
+// lane waits and counts, one elected lane issues) and walks the CTA's step sequence on its own; what orders them is the s_free barrier (S(g) may overwrite an accumulator only after
+// the P.V that read the P bytes in it has completed) and, through the softmax warps, s_full -> p_ready.
+// A wait that gives up only notes which one it was; the status is raised once, after the loop.
+struct IssuerErr {
+  uint32_t code = 0u, tile = 0u;
+};
+template <bool kSlow = false>
+__device__ __forceinline__ bool issuer_wait(IssuerErr& e, uint32_t bar, uint32_t parity, uint32_t code, uint32_t tile, const volatile int* abort_flag) {
+  if (__all_sync(0xFFFFFFFFu, kSlow ? mbar_wait_slow(bar, parity, abort_flag) : mbar_wait(bar, parity, abort_flag))) return true;
+  e.code = code;
+  e.tile = tile;
+  return false;
+}
+
+template <int D>
+__device__ __forceinline__ void s_issuer_role(const FwdParams& p, FwdCtl<FwdCfg<D>::kStagesK, FwdCfg<D>::kStagesV>* ctl, const uint32_t tmem_base,
+                                              const uint32_t q_smem, const uint32_t k_smem, const uint32_t bias_a_smem, const uint32_t bias_b_smem,
+                                              const int first_unit, const int unit_step) {
+  using Cfg = FwdCfg<D>;
+  constexpr uint32_t NK = Cfg::kStagesK, NQ = Cfg::kQBufs;
+  volatile int* abort_flag = &ctl->abort;
+  constexpr uint32_t idesc_s = make_idesc_i8(kTile, false);   // S = Q.K^T : N = 128 keys, both K-major
+  constexpr uint32_t idesc_bias_s = make_idesc_f16(kTile);
+  const uint64_t d_bias_a = make_smem_desc_noswizzle(bias_a_smem, 128, 256);
+  const uint64_t d_bias_b = make_smem_desc_noswizzle(bias_b_smem, 128, 256);
+  IssuerErr err;
+  uint32_t g = 0, qn = 0;
+  int it = 0;
+  bool ok = true;
+  for (int u = first_unit; u < p.n_units && ok; u += unit_step, ++it) {
+    const int buf = it % kInfoBufs;
+    if (!issuer_wait<true>(err, smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it / kInfoBufs) & 1), FMHA_I8_DEV_WAIT_INFO, it, abort_flag)) break;
+    const int n_live = ctl->info[buf].n_live;
+    __syncwarp();
+    if (elect_one()) mbar_arrive(smem_u32(&ctl->info_empty[buf]));            // only the tile count is needed here
+    if (n_live == 0) continue;
+    const uint32_t qb = qn % NQ;
+    if (!issuer_wait<true>(err, smem_u32(&ctl->q_full[qb]), (qn / NQ) & 1u, FMHA_I8_DEV_WAIT_Q_LOAD, g, abort_flag)) break;
+    const uint64_t dq = make_smem_desc(q_smem + qb * Cfg::kTileBytes, D);
+    for (int j = 0; j < n_live; ++j, ++g) {
+      const uint32_t sb = g % SBufs<D>::n, stage = g % NK;
+      // the accumulator still holds the P bytes of step g - SBufs<D>::n until that step's P.V has completed
+      if (g >= SBufs<D>::n && !issuer_wait(err, smem_u32(&ctl->s_free[sb]), ((g / SBufs<D>::n) - 1) & 1u, FMHA_I8_DEV_WAIT_O_FREE, g, abort_flag)) { ok = false; break; }
+      if (!issuer_wait<true>(err, smem_u32(&ctl->k_full[stage]), (g / NK) & 1u, FMHA_I8_DEV_WAIT_K_LOAD, g, abort_flag)) { ok = false; break; }
+      FMHA_STAMP(15, g);
+      tc_fence_after();
+      const uint64_t dk = make_smem_desc(k_smem + stage * Cfg::kTileBytes, D);
+      const uint32_t tS = tmem_base + sb * kTile;
+      if (elect_one()) {
+        mma_f16_ss(tS, d_bias_a, d_bias_b, idesc_bias_s, 0u);      // accumulator := 0x4B400000
+#pragma unroll
+        for (int kk = 0; kk < D / 32; ++kk)
+          mma_i8_ss(tS, desc_advance(dq, kk * 32), desc_advance(dk, kk * 32), idesc_s, 1u);
+        mma_commit(smem_u32(&ctl->s_full[sb]));
+        mma_commit(smem_u32(&ctl->k_empty[stage]));
+        if (j == n_live - 1) mma_commit(smem_u32(&ctl->q_empty[qb]));                   // that was the unit's last use of its Q rows
+      }
+      FMHA_STAMP(12, g);
+    }
+    if (!ok) break;
+    ++qn;
+  }
+  if (err.code != 0u && elect_one()) raise_status(abort_flag, p.status, err.code, err.tile);
+}
+
+template <int D>
+__device__ __forceinline__ void o_issuer_role(const FwdParams& p, FwdCtl<FwdCfg<D>::kStagesK, FwdCfg<D>::kStagesV>* ctl, const uint32_t tmem_base,
+                                              const uint32_t v_smem, const uint32_t bias_a_smem, const uint32_t bias_b_smem,
+                                              const int first_unit, const int unit_step) {
+  using Cfg = FwdCfg<D>;
+  constexpr uint32_t NV = Cfg::kStagesV;
+  volatile int* abort_flag = &ctl->abort;
+  constexpr int NMain = D > kOMain ? kOMain : D, NAnnex = D > kOMain ? D - kOMain : 16;
+  static_assert(NAnnex <= kOAnnex, "annex too small");
+  // O = P.V : V is an MN-major operand; N = 96 + 32 output columns for head_dim 128, 64 for head_dim 64
+  const uint32_t idesc_main = p.p_unsigned ? make_idesc_i8(NMain, true, true) : make_idesc_i8(NMain, true, false);
+  const uint32_t idesc_annex = p.p_unsigned ? make_idesc_i8(NAnnex, true, true) : make_idesc_i8(NAnnex, true, false);
+#if FMHA_PV_BIAS_MMA
+  constexpr uint32_t idesc_bias_main = make_idesc_f16(NMain), idesc_bias_annex = make_idesc_f16(NAnnex);
+  const uint64_t d_bias_a = make_smem_desc_noswizzle(bias_a_smem, 128, 256);
+  const uint64_t d_bias_b = make_smem_desc_noswizzle(bias_b_smem, 128, 256);
+#endif
+  IssuerErr err;
+  uint32_t g = 0;
+  int it = 0;
+  bool ok = true;
+  for (int u = first_unit; u < p.n_units && ok; u += unit_step, ++it) {
+    const int buf = it % kInfoBufs;
+    if (!issuer_wait<true>(err, smem_u32(&ctl->info_full[buf]), static_cast<uint32_t>((it / kInfoBufs) & 1), FMHA_I8_DEV_WAIT_INFO, it, abort_flag)) break;
+    const int n_live = ctl->info[buf].n_live;
+    __syncwarp();
+    if (elect_one()) mbar_arrive(smem_u32(&ctl->info_empty[buf]));            // only the tile count is needed here
+    for (int j = 0; j < n_live; ++j, ++g) {
+      const uint32_t sb = g % SBufs<D>::n, stage = g % NV;
+      if (!issuer_wait(err, smem_u32(&ctl->p_ready[g & 3u]), (g >> 2) & 1u, FMHA_I8_DEV_WAIT_P_READY, g, abort_flag)) { ok = false; break; }
+      FMHA_STAMP(13, g);
+      if (!issuer_wait<true>(err, smem_u32(&ctl->v_full[stage]), (g / NV) & 1u, FMHA_I8_DEV_WAIT_V_LOAD, g, abort_flag)) { ok = false; break; }
+      const uint64_t dv = make_smem_desc(v_smem + stage * Cfg::kTileBytes, D);
+      const uint32_t tP = tmem_base + sb * kTile;
+      tc_fence_after();
+      // The accumulator of this step is the part of S(g)'s own buffer that holds no P bytes (free since the softmax
+      // threads have read S(g)) plus, for head_dim 128, that buffer's annex (free since S(g) could be issued at all).
+      if (elect_one()) {
+#pragma unroll
+      for (int part = 0; part < (D > kOMain ? 2 : 1); ++part) {
+        const int col0 = part * kOMain;                                  // first output column of this part
+        const uint32_t tO = part == 0 ? (tP + kOOff) : (tmem_base + SBufs<D>::n * kTile + sb * kOAnnex);
+        const uint32_t idesc_o = part == 0 ? idesc_main : idesc_annex;
+#if FMHA_PV_BIAS_MMA
+        mma_f16_ss(tO, d_bias_a, d_bias_b, part == 0 ? idesc_bias_main : idesc_bias_annex, 0u);      // accumulator := 0x4B400000
+#endif
+#pragma unroll
+        for (int kk = 0; kk < kTile / 32; ++kk)     // keys 32 kk ...: P bytes of keys 0-63 at columns 0-15, of keys 64-127 at columns 112-127
+          mma_i8_ts(tO, tP + (kk >> 1) * 112 + (kk & 1) * 8, desc_advance(dv, kk * 32 * D + col0), idesc_o, (FMHA_PV_BIAS_MMA || kk > 0) ? 1u : 0u);
+      }
+      mma_commit(smem_u32(&ctl->o_full[sb]));
+      mma_commit(smem_u32(&ctl->v_empty[stage]));
+      }
+      FMHA_STAMP(14, g);
+    }
+  }
+  if (err.code != 0u && elect_one()) raise_status(abort_flag, p.status, err.code, err.tile);
 }
 
 // Persistent kernel: gridDim.x = min(units, SMs) CTAs; CTA b processes units b, b + gridDim.x, ...
@@ -654,7 +832,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
   using Cfg = FwdCfg<D>;
-  constexpr int NK = Cfg::kStagesK, NV = Cfg::kStagesV, NQ = Cfg::kQBufs, DH = D / 2;
+  constexpr int NK = Cfg::kStagesK, NV = Cfg::kStagesV, NQ = Cfg::kQBufs;
   using Ctl = FwdCtl<NK, NV>;
   extern __shared__ uint8_t smem_raw[];
   // tiles need 1024-byte alignment (swizzle atoms); the launch reserves the slack
@@ -676,12 +854,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(smem_u32(&ctl->q_full[w]), 1);
       mbar_init(smem_u32(&ctl->q_empty[w]), 1);
     }
-    for (int w = 0; w < 2; ++w) {
-      mbar_init(smem_u32(&ctl->o_full[w]), 1);
-      mbar_init(smem_u32(&ctl->o_free[w]), 4 * 32);
+    for (int w = 0; w < 2; ++w)
       for (int q = 0; q < 4; ++q) mbar_init(smem_u32(&ctl->xch[w][q]), 64);
+    for (int s = 0; s < SBufs<D>::n; ++s) {
+      mbar_init(smem_u32(&ctl->s_full[s]), 1);
+      mbar_init(smem_u32(&ctl->o_full[s]), 1);
+      mbar_init(smem_u32(&ctl->s_free[s]), kMergeWarps * 32);
     }
-    for (int s = 0; s < kSBufs; ++s) mbar_init(smem_u32(&ctl->s_full[s]), 1);
     for (int s = 0; s < NK; ++s) {
       mbar_init(smem_u32(&ctl->k_full[s]), 1);
       mbar_init(smem_u32(&ctl->k_empty[s]), 1);
@@ -714,104 +893,20 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   // Every role walks the same unit sequence: `it` counts this CTA's units, info buffer = it % kInfoBufs,
   // phase of an info barrier = (it / kInfoBufs) & 1; `g` counts its steps (live key tiles) across units.
-  if (warp < kSoftmaxWarps) {
-    setmaxnreg_dec<FwdRegs::kSoftmax>();
+  if (warp >= kWarpSoftmax0) {
+    setmaxnreg_dec<FwdRegs<D>::kSoftmax>();
     softmax_role<D>(p, ctl, tmem_base, first_unit, unit_step);
-  } else if (warp < kWarpLoadK) {
-    setmaxnreg_inc<FwdRegs::kMerge>();
+  } else if (warp >= kWarpMerge0) {
+    setmaxnreg_inc<FwdRegs<D>::kMerge>();
     merge_role<D>(p, ctl, tmem_base, first_unit, unit_step);
   } else {
-    setmaxnreg_dec<FwdRegs::kOther>();
-    if (warp == kWarpLoadK) {
-      if (lane == 0) loader_role<D, true>(p, ctl, &map_q, &map_k, q_smem, k_smem, first_unit, unit_step);
-    } else if (warp == kWarpLoadV) {
-      if (lane == 0) loader_role<D, false>(p, ctl, &map_q, &map_v, q_smem, v_smem, first_unit, unit_step);
-    } else if (warp == kWarpMma) {
-      // ---------------------------------------------------------------- MMA issuer
-      if (lane == 0) {
-        constexpr uint32_t idesc_s = make_idesc_i8(kTile, false);   // S = Q.K^T : N = 128 keys, both K-major
-        const uint32_t idesc_o = p.p_unsigned ? make_idesc_i8(DH, true, true) : make_idesc_i8(DH, true, false);   // O = P.V : N = D/2, V is MN-major
-        constexpr uint32_t idesc_bias_s = make_idesc_f16(kTile);
-        const uint64_t d_bias_a = make_smem_desc_noswizzle(smem_u32(bias_a), 128, 256);
-        const uint64_t d_bias_b = make_smem_desc_noswizzle(smem_u32(bias_b), 128, 256);
-        // A wait that gives up only notes which one it was; the status is raised once, after the loop.
-        uint32_t err = 0u, err_tile = 0u;
-        auto wait = [&](uint32_t bar, uint32_t parity, uint32_t code, uint32_t tile) -> bool {
-          if (mbar_wait(bar, parity, abort_flag)) return true;
-          err = code;
-          err_tile = tile;
-          return false;
-        };
-        // The S cursor walks the CTA's step sequence kSBufs steps ahead of the P.V counter gp; it is valid
-        // while its unit index is below n_units.  It releases the mask information of every unit it leaves.
-        int s_u = first_unit - unit_step, s_it = -1, s_j = 0, s_nl = 0;
-        uint32_t gs = 0, gp = 0, qn = 0;
-        bool ok = true;
-        auto next_unit = [&]() -> bool {
-          for (;;) {
-            if (s_it >= 0) mbar_arrive(smem_u32(&ctl->info_empty[s_it % kInfoBufs]));
-            s_u += unit_step;
-            ++s_it;
-            if (s_u >= p.n_units) return true;
-            if (!wait(smem_u32(&ctl->info_full[s_it % kInfoBufs]), static_cast<uint32_t>((s_it / kInfoBufs) & 1), FMHA_I8_DEV_WAIT_INFO, s_it)) return false;
-            s_nl = ctl->info[s_it % kInfoBufs].n_live;
-            if (s_nl > 0) return true;
-          }
-        };
-        auto issue_s = [&]() -> bool {
-          const uint32_t sb = gs % kSBufs, stage = gs % NK, qb = qn % NQ;
-          if (s_j == 0 && !wait(smem_u32(&ctl->q_full[qb]), (qn / NQ) & 1u, FMHA_I8_DEV_WAIT_Q_LOAD, gs)) return false;
-          if (!wait(smem_u32(&ctl->k_full[stage]), (gs / NK) & 1u, FMHA_I8_DEV_WAIT_K_LOAD, gs)) return false;
-          FMHA_STAMP(15, gs);
-          tc_fence_after();
-          const uint64_t dq = make_smem_desc(q_smem + qb * Cfg::kTileBytes, D);
-          const uint64_t dk = make_smem_desc(k_smem + stage * Cfg::kTileBytes, D);
-          const uint32_t tS = tmem_base + sb * kTile;
-          mma_f16_ss(tS, d_bias_a, d_bias_b, idesc_bias_s, 0u);      // accumulator := 0x4B400000
-#pragma unroll
-          for (int kk = 0; kk < D / 32; ++kk)
-            mma_i8_ss(tS, desc_advance(dq, kk * 32), desc_advance(dk, kk * 32), idesc_s, 1u);
-          mma_commit(smem_u32(&ctl->s_full[sb]));
-          mma_commit(smem_u32(&ctl->k_empty[stage]));
-          FMHA_STAMP(12, gs);
-          ++gs;
-          if (++s_j == s_nl) {
-            mma_commit(smem_u32(&ctl->q_empty[qb]));                 // that was the unit's last use of its Q rows
-            ++qn;
-            s_j = 0;
-            return next_unit();
-          }
-          return true;
-        };
-        ok = next_unit();
-        for (int i = 0; i < kSBufs && ok && s_u < p.n_units; ++i) ok = issue_s();
-        while (ok && gp < gs) {
-          const uint32_t sb = gp % kSBufs, stage = gp % NV;
-          if (!wait(smem_u32(&ctl->p_ready[gp & 3u]), (gp >> 2) & 1u, FMHA_I8_DEV_WAIT_P_READY, gp)) { ok = false; break; }
-          FMHA_STAMP(13, gp);
-          if (!wait(smem_u32(&ctl->v_full[stage]), (gp / NV) & 1u, FMHA_I8_DEV_WAIT_V_LOAD, gp)) { ok = false; break; }
-          const uint64_t dv = make_smem_desc(v_smem + stage * Cfg::kTileBytes, D);
-          const uint32_t tP = tmem_base + sb * kTile;
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            // the accumulator of this half is free once the merge threads have drained the previous step's half
-            if (gp > 0 && !wait(smem_u32(&ctl->o_free[h]), (gp - 1) & 1u, FMHA_I8_DEV_WAIT_O_FREE, gp)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t tO = tmem_base + kSBufs * kTile + h * DH;
-#pragma unroll
-            for (int kk = 0; kk < kTile / 32; ++kk)     // keys 32 kk ...: P bytes of keys 0-63 at columns 0-15, of keys 64-127 at columns 64-79
-              mma_i8_ts(tO, tP + (kk >> 1) * kHalf + (kk & 1) * 8, desc_advance(dv, kk * 32 * D + h * DH), idesc_o, kk > 0 ? 1u : 0u);
-            mma_commit(smem_u32(&ctl->o_full[h]));
-          }
-          if (!ok) break;
-          mma_commit(smem_u32(&ctl->v_empty[stage]));
-          FMHA_STAMP(14, gp);
-          ++gp;
-          // the S / P columns of that step are free again (the tensor pipe runs this thread's MMAs in order)
-          if (s_u < p.n_units) ok = issue_s();
-        }
-        if (err != 0u) raise_status(abort_flag, p.status, err, err_tile);
-      }
+    if (FwdRegs<D>::kOther < kLaunchRegs) setmaxnreg_dec<FwdRegs<D>::kOther>(); else setmaxnreg_inc<FwdRegs<D>::kOther>();
+    if (warp == kWarpLoad) {
+      loader_role<D>(p, ctl, &map_q, &map_k, &map_v, q_smem, k_smem, v_smem, first_unit, unit_step);
+    } else if (warp == kWarpMmaS) {
+      s_issuer_role<D>(p, ctl, tmem_base, q_smem, k_smem, smem_u32(bias_a), smem_u32(bias_b), first_unit, unit_step);
+    } else if (warp == kWarpMmaO) {
+      o_issuer_role<D>(p, ctl, tmem_base, v_smem, smem_u32(bias_a), smem_u32(bias_b), first_unit, unit_step);
     } else if (warp == kWarpScan) {
       // ---------------------------------------------------------------- scanner: mask information, units ahead
       bool ok = true;
@@ -820,7 +915,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const int buf = it % kInfoBufs;
         // the buffer was used by unit it - kInfoBufs: wait until all its consumers have released it
         if (it >= kInfoBufs) {
-          ok = __all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&ctl->info_empty[buf]), static_cast<uint32_t>(((it / kInfoBufs) - 1) & 1), abort_flag));
+          ok = __all_sync(0xFFFFFFFFu, mbar_wait_slow(smem_u32(&ctl->info_empty[buf]), static_cast<uint32_t>(((it / kInfoBufs) - 1) & 1), abort_flag));
           if (!ok) { if (lane == 0) raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_INFO, it); break; }
         }
         const UnitGeom geo = unit_geom(p, u);

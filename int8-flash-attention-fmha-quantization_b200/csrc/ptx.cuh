@@ -56,22 +56,62 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 // About one second at boost clock.  No legitimate wait in these kernels is longer than the time
 // one CTA needs for one key tile (microseconds).
 constexpr long long kWaitLimitCycles = 2000000000LL;
+// A wait only gives up after this many probes as well: the cycle counter keeps running while the context is
+// switched out on a shared GPU, probes do not, so a long time slice elsewhere cannot by itself end a wait.
+constexpr uint32_t kMinProbes = 4096u;
 
-// Waits for the phase with the given parity to complete.  Gives up when the cycle limit is reached
-// or when another thread of the CTA has already raised *abort_flag.
-__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, const volatile int* abort_flag, long long limit_cycles) {
+// Back-off between probes, in nanoseconds (0 = none, the default and the measured best).  mbarrier.try_wait returns
+// after a short, hardware-defined time when the phase is not complete, so a waiting warp keeps issuing its polling
+// loop.  nanosleep between probes was measured on B200 to cost more on the hand-offs than the freed issue slots are
+// worth (and every argument up to 80 ns sleeps equally long); the two classes of waits -- on the step-to-step
+// critical path, and normally satisfied long before they are needed -- are kept apart for further tuning.
+#ifndef FMHA_SLEEP_FAST
+#define FMHA_SLEEP_FAST 0
+#endif
+#ifndef FMHA_SLEEP_SLOW
+#define FMHA_SLEEP_SLOW 0
+#endif
+
+// Waits for the phase with the given parity to complete.  Gives up when the cycle limit is reached (and at
+// least min_probes probes were made) or when another thread of the CTA has already raised *abort_flag.
+// The loop is deliberately not tight: measured on B200, a waiting warp that probes as fast as it can (three
+// instructions per probe) slows the working warps of its SM down more than this one does, and nanosleep between
+// probes costs more latency on the hand-offs than it saves (any argument up to 80 ns sleeps equally long).
+template <uint32_t kSleepNs>
+__device__ __forceinline__ bool mbar_wait_backoff(uint32_t bar, uint32_t parity, const volatile int* abort_flag, long long limit_cycles,
+                                                  uint32_t min_probes) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
+    if (kSleepNs != 0u) __nanosleep(kSleepNs);
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 31u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > limit_cycles) return false;
+      if (it >= min_probes && clock64() - t0 > limit_cycles) return false;
     }
   }
 }
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, const volatile int* abort_flag, long long limit_cycles) {
+  return mbar_wait_backoff<0u>(bar, parity, abort_flag, limit_cycles, 0u);
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
-  return mbar_wait_limited(bar, parity, abort_flag, kWaitLimitCycles);
+  return mbar_wait_backoff<FMHA_SLEEP_FAST>(bar, parity, abort_flag, kWaitLimitCycles, kMinProbes);
+}
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+  return mbar_wait_backoff<FMHA_SLEEP_SLOW>(bar, parity, abort_flag, kWaitLimitCycles, kMinProbes);
+}
+
+// One lane of a converged warp (the same one every time).  The single-thread roles of the forward kernel run
+// warp-wide with only their side-effecting instructions behind this predicate: addresses, descriptors and loop
+// counters are then warp-uniform values.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xFFFFFFFF;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 // ---------------------------------------------------------------- TMA
