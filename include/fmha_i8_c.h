@@ -92,6 +92,27 @@ int fmha_i8_sm100_infer_cross(void* stream, const float amax[5], const int desc5
                               const void* q, const void* k, const void* v, const void* mask, void* o,
                               int bh_begin, int bh_count, unsigned flags);
 
+/* Whole-row scaling policies for the 8-bit P, the subject of the reference's accuracy study
+ * (fmha_i8_quant_deviation.py:57-121, fmha_i8_quant_error_seqlen.py, README.md:192-222) and absent from its kernel,
+ * which quantises P against the maximum of each 128-key tile.
+ *   FMHA_I8_POLICY_TILE    the reference kernel's arithmetic: identical to fmha_i8_sm100_infer_cross
+ *   FMHA_I8_POLICY_ROW     "dynamic quantization": P8 = rn(127 p / p_amax_row), p_amax_row = the row's largest
+ *                          probability (fmha_i8_quant_deviation.py:104-121)
+ *   FMHA_I8_POLICY_STATIC  "static quantization": P8 = min(rn(127 p / s_max), 127) with ONE calibrated scale for
+ *                          every row: amax[4] = s_max, the FMHAParamI8 field the reference fills
+ *                          (test_fmha_i8.cpp:152) and never reads (README.md:27; :82-102 of the script)
+ * P is unsigned with 127 levels as in the study.  A row's scale is only known when all its keys have been seen, so
+ * the call makes two launches on `stream`: the first computes every row's maximum and exp-sum, the second
+ * quantises and multiplies.  row_scratch: caller-owned device memory, 2 floats per query row of the slice
+ * (8 * bh_count * seq_len_q bytes, 8-byte aligned); nothing is allocated.  Other arguments as in
+ * fmha_i8_sm100_infer_cross; FMHA_I8_FLAG_UINT8_P is not accepted. */
+#define FMHA_I8_POLICY_TILE 0
+#define FMHA_I8_POLICY_ROW 1
+#define FMHA_I8_POLICY_STATIC 2
+int fmha_i8_sm100_infer_policy(void* stream, const float amax[5], const int desc5[5],
+                               const void* q, const void* k, const void* v, const void* mask, void* o,
+                               int bh_begin, int bh_count, unsigned flags, int policy, float* row_scratch);
+
 /* Calibration of o_amax on the device.  The reference takes o_amax = max|O| from its fp32 CPU attention
  * (test_fmha_i8.cpp:161) before it can call the int8 kernel at all; this runs the same int8 pipeline
  * (same kernel, same tiles) but instead of storing O8 it writes the largest magnitude of the unquantised

@@ -32,7 +32,7 @@ FLAG_UINT8_P = 2     # P quantised as unsigned 8 bit, 255 levels (the reference 
 
 EXPORTS = (
     "fmha_i8_sm100_infer", "fmha_i8_sm100_infer_slice", "fmha_i8_sm100_infer_cross", "fmha_i8_sm100_calibrate_o_amax", "fmha_i8_sm100_infer_host",
-    "fmha_i8_sm100_infer_host_slice",
+    "fmha_i8_sm100_infer_host_slice", "fmha_i8_sm100_infer_policy",
     "fmha_i8_sm100_debug_qk", "fmha_i8_sm100_debug_pv", "fmha_i8_sm100_debug_simt", "fmha_i8_sm100_debug_simt_x", "fmha_i8_sm100_debug_wait_probe",
     "fmha_i8_sm100_quantize_f32", "fmha_i8_sm100_quantize_f32_noalloc", "fmha_i8_sm100_device_status", "fmha_i8_sm100_last_status", "fmha_i8_sm100_status_string",
     "fmha_i8_sm100_launch_count", "fmha_i8_sm100_version",
@@ -99,6 +99,7 @@ def lib():
         L.fmha_i8_sm100_infer_slice.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, u]
         L.fmha_i8_sm100_infer_cross.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, u]
         L.fmha_i8_sm100_calibrate_o_amax.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, u]
+        L.fmha_i8_sm100_infer_policy.argtypes = [vp, fp, ip, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, u, ctypes.c_int, vp]
         L.fmha_i8_sm100_infer_host.argtypes = [fp, ip, vp, vp, vp, vp, vp, u]
         L.fmha_i8_sm100_infer_host_slice.argtypes = [fp, ip, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, u]
         L.fmha_i8_sm100_debug_qk.argtypes = [vp, ip, vp, vp, vp]
@@ -173,6 +174,24 @@ def FMHAInferI8Cross(stream, fmha_param, attn_desc_x, q, k, v, padding_mask, o, 
                                          _flags(use_tcu, uint8_p))
     if check and st != OK:
         raise FmhaError(st, "FMHAInferI8Cross")
+    return st
+
+
+POLICY_TILE, POLICY_ROW, POLICY_STATIC = 0, 1, 2
+
+
+def FMHAInferI8Policy(stream, fmha_param, attn_desc_x, q, k, v, padding_mask, o, policy, row_scratch, bh_begin=0, bh_count=None,
+                      check=True):
+    """Whole-row scaling policies for the 8-bit P (reference fmha_i8_quant_deviation.py:57-121): POLICY_ROW = per-row
+    ("dynamic") scale, POLICY_STATIC = one calibrated scale fmha_param.s_max for all rows, POLICY_TILE = the reference
+    kernel's tile-local scale.  row_scratch: float32 device tensor with 2 elements per query row of the slice."""
+    if bh_count is None:
+        bh_count = attn_desc_x.batch_num * attn_desc_x.head_num - bh_begin
+    st = lib().fmha_i8_sm100_infer_policy(_stream_handle(stream), fmha_param.as_c(), attn_desc_x.as_c(), _ptr(q), _ptr(k), _ptr(v),
+                                          _ptr(padding_mask), _ptr(o), int(bh_begin), int(bh_count), _flags(True, False),
+                                          int(policy), _ptr(row_scratch))
+    if check and st != OK:
+        raise FmhaError(st, "FMHAInferI8Policy")
     return st
 
 

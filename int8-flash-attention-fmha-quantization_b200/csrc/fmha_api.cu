@@ -96,8 +96,10 @@ int set_kernel_attributes(DeviceInfo* d) {
   auto set = [&](const void* fn, size_t bytes) {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
   };
-  set(reinterpret_cast<const void*>(&fmha_fwd_kernel<64>), fwd_smem_bytes<64>());
-  set(reinterpret_cast<const void*>(&fmha_fwd_kernel<128>), fwd_smem_bytes<128>());
+  set(reinterpret_cast<const void*>(&fmha_fwd_kernel<64, false>), fwd_smem_bytes<64>());
+  set(reinterpret_cast<const void*>(&fmha_fwd_kernel<128, false>), fwd_smem_bytes<128>());
+  set(reinterpret_cast<const void*>(&fmha_fwd_kernel<64, true>), fwd_smem_bytes<64>());
+  set(reinterpret_cast<const void*>(&fmha_fwd_kernel<128, true>), fwd_smem_bytes<128>());
   set(reinterpret_cast<const void*>(&debug_qk_kernel<64>), qk_smem_bytes<64>());
   set(reinterpret_cast<const void*>(&debug_qk_kernel<128>), qk_smem_bytes<128>());
   set(reinterpret_cast<const void*>(&debug_pv_kernel<64, true>), pv_smem_bytes<64>());
@@ -107,10 +109,12 @@ int set_kernel_attributes(DeviceInfo* d) {
   if (e != cudaSuccess) { cudaGetLastError(); return FMHA_I8_ERR_LAUNCH; }
   // The forward kernel redistributes registers with setmaxnreg; that only terminates if the launch
   // allocation is the one the targets were sized for.
-  cudaFuncAttributes fa64{}, fa128{};
-  if (cudaFuncGetAttributes(&fa64, reinterpret_cast<const void*>(&fmha_fwd_kernel<64>)) != cudaSuccess ||
-      cudaFuncGetAttributes(&fa128, reinterpret_cast<const void*>(&fmha_fwd_kernel<128>)) != cudaSuccess ||
-      fa64.numRegs != kLaunchRegs || fa128.numRegs != kLaunchRegs) {
+  cudaFuncAttributes fa64{}, fa128{}, fp64{}, fp128{};
+  if (cudaFuncGetAttributes(&fa64, reinterpret_cast<const void*>(&fmha_fwd_kernel<64, false>)) != cudaSuccess ||
+      cudaFuncGetAttributes(&fa128, reinterpret_cast<const void*>(&fmha_fwd_kernel<128, false>)) != cudaSuccess ||
+      cudaFuncGetAttributes(&fp64, reinterpret_cast<const void*>(&fmha_fwd_kernel<64, true>)) != cudaSuccess ||
+      cudaFuncGetAttributes(&fp128, reinterpret_cast<const void*>(&fmha_fwd_kernel<128, true>)) != cudaSuccess ||
+      fa64.numRegs != kLaunchRegs || fa128.numRegs != kLaunchRegs || fp64.numRegs != kLaunchRegs || fp128.numRegs != kLaunchRegs) {
     cudaGetLastError();
     std::fprintf(stderr, "fmha_i8_sm100: forward kernel built with %d/%d registers per thread, expected %d; refusing to launch\n",
                  fa64.numRegs, fa128.numRegs, kLaunchRegs);
@@ -202,7 +206,7 @@ int fill_params(FwdParams* p, const float amax[5], int D, unsigned flags = 0u) {
   return FMHA_I8_OK;
 }
 
-template <int D>
+template <int D, bool kPolicy = false>
 int launch_fwd(cudaStream_t stream, DeviceInfo* dev, FwdParams p, const void* q, const void* k, const void* v) {
   CUtensorMap mq, mk, mv;
   int st;
@@ -211,16 +215,25 @@ int launch_fwd(cudaStream_t stream, DeviceInfo* dev, FwdParams p, const void* q,
   if ((st = make_map(&mv, v, p.bh_count, p.S, D)) != FMHA_I8_OK) return st;
   // persistent CTAs: one per SM (tensor memory is allocated whole), each walking its share of the units
   const unsigned grid = static_cast<unsigned>(p.n_units < dev->sm_count ? p.n_units : dev->sm_count);
-  fmha_fwd_kernel<D><<<grid, kFwdThreads, fwd_smem_bytes<D>(), stream>>>(mq, mk, mv, p);
+  fmha_fwd_kernel<D, kPolicy><<<grid, kFwdThreads, fwd_smem_bytes<D>(), stream>>>(mq, mk, mv, p);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? FMHA_I8_OK : FMHA_I8_ERR_LAUNCH;
 }
 
 // calib == nullptr: the forward pass into o.  calib != nullptr: calibration, o is not touched (may be null).
+// Which of the three uses of the forward kernel a launch is.
+struct LaunchMode {
+  float* calib = nullptr;          // calibration: largest |output| to this device float, o untouched
+  float2* stats_out = nullptr;     // statistics launch of a whole-row policy: {row max bits, exp-sum} per query row, o untouched
+  const float2* stats_in = nullptr;  // policy launch: those statistics
+  int policy = 0;                  // FMHA_I8_POLICY_* of a policy launch
+};
+
 int infer_x_impl(void* stream, const float amax[5], const Shape& sh, const void* q, const void* k,
                  const void* v, const void* mask, void* o, int bh_begin, int bh_count, unsigned flags,
-                 float* calib = nullptr) {
-  if (!amax || !q || !k || !v || !mask || (!o && !calib)) return FMHA_I8_ERR_NULL_POINTER;
+                 float* calib = nullptr, const LaunchMode* mode = nullptr) {
+  const bool no_output = calib || (mode && mode->stats_out);
+  if (!amax || !q || !k || !v || !mask || (!o && !no_output)) return FMHA_I8_ERR_NULL_POINTER;
   if (!(flags & FMHA_I8_FLAG_USE_TCU)) return FMHA_I8_ERR_NO_CUDA_CORE_PATH;
   if (flags & ~(FMHA_I8_FLAG_USE_TCU | FMHA_I8_FLAG_UINT8_P)) return FMHA_I8_ERR_BAD_FLAGS;
   int st = check_shape_x(sh);
@@ -232,6 +245,26 @@ int infer_x_impl(void* stream, const float amax[5], const Shape& sh, const void*
   FwdParams p{};
   if ((st = fill_params(&p, amax, sh.D, flags)) != FMHA_I8_OK) return st;
   p.amax_out = calib;
+  const bool policy_launch = mode && mode->stats_in;
+  if (mode) {
+    p.row_stats_out = mode->stats_out;
+    p.row_stats_in = mode->stats_in;
+    if (policy_launch) {
+      // fmha_i8_quant_deviation.py:7,38-43: 127 levels, unsigned, P8 = clip(rn(p * 127 / p_amax), 0, 127).
+      // Per-row ("dynamic", :104-118): p_amax = the row's largest probability = 1/l, so P8 = rn(127 e) and the output
+      // is (sum P8 v8) / (127 l) * v_amax/127.  Static (:82-98): p_amax = s_max for every row, so
+      // P8 = min(rn(127 e / (l s_max)), 127) and the output is (sum P8 v8) * s_max/127 * v_amax/127.
+      const float levels = 127.f;
+      if (mode->policy == FMHA_I8_POLICY_STATIC && (!(amax[4] > 0.f) || !std::isfinite(amax[4]))) return FMHA_I8_ERR_BAD_AMAX;
+      p.p_levels = levels;
+      p.p_row_mul = levels;
+      p.p_static_mul = (mode->policy == FMHA_I8_POLICY_STATIC) ? levels / amax[4] : 0.f;
+      p.p_mul = levels;
+      p.o_sign = 1.f;
+      p.p_unsigned = 1u;
+      p.scale_v_out = (mode->policy == FMHA_I8_POLICY_STATIC) ? amax[4] * amax[2] / (levels * amax[3]) : amax[2] / (levels * amax[3]);
+    }
+  }
   int err = FMHA_I8_OK;
   DeviceInfo* dev = current_device(&err);
   if (!dev) return err;
@@ -257,6 +290,7 @@ int infer_x_impl(void* stream, const float amax[5], const Shape& sh, const void*
   }
   p.status = dev->status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (policy_launch) return sh.D == 128 ? launch_fwd<128, true>(s, dev, p, q, k, v) : launch_fwd<64, true>(s, dev, p, q, k, v);
   return sh.D == 128 ? launch_fwd<128>(s, dev, p, q, k, v) : launch_fwd<64>(s, dev, p, q, k, v);
 }
 
@@ -333,6 +367,28 @@ int fmha_i8_sm100_infer_cross(void* stream, const float amax[5], const int desc5
   if (!desc5) return finish(FMHA_I8_ERR_NULL_POINTER);
   const Shape sh{desc5[0], desc5[1], desc5[2], desc5[3], desc5[4]};
   return finish(infer_x_impl(stream, amax, sh, q, k, v, mask, o, bh_begin, bh_count, flags));
+}
+
+int fmha_i8_sm100_infer_policy(void* stream, const float amax[5], const int desc5[5], const void* q, const void* k,
+                               const void* v, const void* mask, void* o, int bh_begin, int bh_count, unsigned flags,
+                               int policy, float* row_scratch) {
+  if (!desc5) return finish(FMHA_I8_ERR_NULL_POINTER);
+  const Shape sh{desc5[0], desc5[1], desc5[2], desc5[3], desc5[4]};
+  if (policy == FMHA_I8_POLICY_TILE) return finish(infer_x_impl(stream, amax, sh, q, k, v, mask, o, bh_begin, bh_count, flags));
+  if (policy != FMHA_I8_POLICY_ROW && policy != FMHA_I8_POLICY_STATIC) return finish(FMHA_I8_ERR_BAD_FLAGS);
+  if (flags & FMHA_I8_FLAG_UINT8_P) return finish(FMHA_I8_ERR_BAD_FLAGS);       // the policies bring their own P format
+  if (!row_scratch || !o) return finish(FMHA_I8_ERR_NULL_POINTER);
+  if (!aligned(row_scratch, 8)) return finish(FMHA_I8_ERR_MISALIGNED);
+  // launch 1: the forward pass with the reference's tile-local arithmetic, keeping only each row's maximum and exp-sum
+  LaunchMode stats;
+  stats.stats_out = reinterpret_cast<float2*>(row_scratch);
+  int st = infer_x_impl(stream, amax, sh, q, k, v, mask, nullptr, bh_begin, bh_count, flags, nullptr, &stats);
+  if (st != FMHA_I8_OK) return finish(st);
+  // launch 2 (same stream, so ordered behind launch 1): every tile of a row quantised with the row's one scale
+  LaunchMode apply;
+  apply.stats_in = reinterpret_cast<const float2*>(row_scratch);
+  apply.policy = policy;
+  return finish(infer_x_impl(stream, amax, sh, q, k, v, mask, o, bh_begin, bh_count, flags, nullptr, &apply));
 }
 
 int fmha_i8_sm100_calibrate_o_amax(void* stream, const float amax[5], const int desc5[5], const void* q, const void* k,

@@ -170,6 +170,14 @@ struct FwdParams {
                         // in real units, max |O~ / l| * amax_scale, is folded into this device float
   float amax_scale;     // v_amax / (127 * 128)  (127 * 255 with unsigned P)
   unsigned* status;     // eight device status words
+  // Whole-row P scaling policies (the reference's accuracy study, fmha_i8_quant_deviation.py:57-121), two launches:
+  float2* row_stats_out;       // statistics launch: per query row {bits of the biased integer row maximum over ALL keys,
+                               // sum over all keys of exp(score - row maximum)} is written here, nothing to o
+  const float2* row_stats_in;  // policy launch (kernel instantiated with kPolicy): those statistics, read back
+  float p_row_mul;      // policy launch: P8 = rn(p_row_mul * exp(score - row max))                  ("dynamic", per-row scale), or
+  float p_static_mul;   //                P8 = min(rn(p_static_mul * exp(score - row max) / l), levels)  ("static" scale; 0 = dynamic)
+  float p_levels;       // quantisation levels of P in a policy launch (127 in the reference's study)
+                        // (a policy launch sets scale_v_out to the factor that turns sum_j P8 v8 [/ l] into int8 output units)
 };
 
 // What every role needs to know about one work unit's padding mask.  kInfoBufs of these live in shared
@@ -194,6 +202,7 @@ template <int NK, int NV> struct FwdCtl {
   int abort;
   // row statistics of a step, written by the softmax threads and read by the merge threads (slot = g & 3)
   float st_m[4][kTile], st_f[4][kTile], st_s0[4][kTile], st_s1[4][kTile];
+  int st_i[4][kTile];                  // biased integer row maximum of the step's tile (for the statistics launch)
   int xmax[2][2][2][kTile];            // [chain][step parity][half][row]: biased integer maximum of that half row
   UnitInfo info[kInfoBufs];
 };
@@ -302,9 +311,10 @@ __device__ __forceinline__ void chunk_max(const uint32_t (&r)[N], uint32_t mw, i
 
 // N scores -> N probabilities (summed into two independent packed accumulators) -> N/4 words of
 // packed bytes holding -rn(128 p) (or rn(255 p)).  x = raw accumulator read as float = kMagic + s.
-template <bool kMixed, int N>
+// kCap: p is limited to p_cap before it is quantised (the static policy clips at its top level, fmha_i8_quant_deviation.py:38-43).
+template <bool kMixed, int N, bool kCap = false>
 __device__ __forceinline__ void chunk_exp_pack(const uint32_t (&r)[N], uint32_t mw, const float2 c2, const float2 neg_hi,
-                                               const float2 p_mul_f, float2 (&sum)[2], uint32_t (&packed)[N / 4]) {
+                                               const float2 p_mul_f, float2 (&sum)[2], uint32_t (&packed)[N / 4], const float p_cap = 0.f) {
   const float2 magic2 = make_float2(kMagic, kMagic);
 #pragma unroll
   for (int g = 0; g < N / 4; ++g) {
@@ -318,8 +328,12 @@ __device__ __forceinline__ void chunk_exp_pack(const uint32_t (&r)[N], uint32_t 
     }
     const float2 a01 = __ffma2_rn(x01, c2, neg_hi);
     const float2 a23 = __ffma2_rn(x23, c2, neg_hi);
-    const float2 p01 = make_float2(ex2_approx(a01.x), ex2_approx(a01.y));
-    const float2 p23 = make_float2(ex2_approx(a23.x), ex2_approx(a23.y));
+    float2 p01 = make_float2(ex2_approx(a01.x), ex2_approx(a01.y));
+    float2 p23 = make_float2(ex2_approx(a23.x), ex2_approx(a23.y));
+    if (kCap) {
+      p01.x = fminf(p01.x, p_cap); p01.y = fminf(p01.y, p_cap);
+      p23.x = fminf(p23.x, p_cap); p23.y = fminf(p23.y, p_cap);
+    }
     sum[0] = __fadd2_rn(sum[0], p01);
     sum[1] = __fadd2_rn(sum[1], p23);
     const float2 y01 = __ffma2_rn(p01, p_mul_f, magic2);      // low byte = the two's-complement P8
@@ -383,7 +397,7 @@ __device__ __forceinline__ UnitGeom unit_geom(const FwdParams& p, int u) {
 // ---------------------------------------------------------------------------------------------- softmax role
 // One thread = one half (64 keys) of one query row of one chain.  Walks the CTA's step sequence and
 // handles the steps of its chain.
-template <int D>
+template <int D, bool kPolicy>
 __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D>::kStagesK, FwdCfg<D>::kStagesV>* ctl, const uint32_t tmem_base,
                                              const int first_unit, const int unit_step) {
   const int warp = (threadIdx.x >> 5) - kWarpSoftmax0, lane = threadIdx.x & 31;
@@ -406,6 +420,21 @@ __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D
     }
     const UnitInfo* info = &ctl->info[buf];
     const int n_live = info->n_live;
+    // Policy launch: the row's maximum over ALL keys and its exp-sum come from the statistics launch; one scale per
+    // row for the whole unit, no tile maximum, no exchange (fmha_i8_quant_deviation.py:62-121).
+    RowConsts kp;
+    float p_cap = 0.f;
+    if (kPolicy) {
+      const UnitGeom geo = unit_geom(p, u);
+      const int q_row = geo.q_row0 + row;
+      float2 st = make_float2(__int_as_float(static_cast<int>(kMagicBits)), 1.f);
+      if (q_row < p.Sq) st = __ldg(&p.row_stats_in[static_cast<int64_t>(geo.bh_local) * p.Sq + q_row]);
+      const float l_row = st.y > 0.f ? st.y : 1.f;
+      // dynamic: P8 = rn(levels * e); static: P8 = min(rn(levels * (e / l) / s_max), levels)
+      const float mul = (p.p_static_mul != 0.f) ? p.p_static_mul / l_row : p.p_row_mul;
+      kp = row_consts(__float_as_int(st.x), c2s, row_scale, scale_qk, mul);
+      p_cap = p.p_levels / kp.p_mul_f.x;        // an exponential above this would quantise beyond the top level
+    }
 #pragma unroll 1
     for (int j = (chain ^ static_cast<int>(g0)) & 1; j < n_live; j += 2, ++n) {
       const uint32_t g = g0 + static_cast<uint32_t>(j);
@@ -428,9 +457,14 @@ __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D
       const int c0 = half ? 3 : 0, cs = half ? -1 : 1;                 // first chunk and direction
       const uint32_t tP = tS + (half ? 48u : 0u);                      // my 16 columns of P
 
+      uint32_t ra[16], rb[16];
+      RowConsts k;
+      if (kPolicy) {
+        k = kp;
+        tmem_ld16_issue(tS + c0 * 16, ra);
+      } else {
       // ---- pass 1: biased integer maximum of my 64 columns (inc/fmha_i8.cuh:183-206)
       int max_a = INT_MIN, max_b = INT_MIN;
-      uint32_t ra[16], rb[16];
       if (!mixed) {
         // two tensor-memory round trips (a round trip costs about as much as the whole arithmetic of this pass)
         uint32_t wide[32];
@@ -459,7 +493,9 @@ __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D
         return;
       }
       const int imax = max(mine, xrow[(half ^ 1) * kTile]);
-      const RowConsts k = row_consts(imax, c2s, row_scale, scale_qk, p_mul);
+      k = row_consts(imax, c2s, row_scale, scale_qk, p_mul);
+      if (half == 0) ctl->st_i[g & 3u][row] = imax;
+      }
       if (half == 0 && quad == 0) FMHA_STAMP(chain * 4 + 1, n);
 
       // ---- pass 2: exp, row sum, requantise, P over columns already consumed (inc/fmha_i8.cuh:208-253)
@@ -467,20 +503,20 @@ __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D
       uint32_t packed[4];
       if (!mixed) {
         tmem_ld_fence(ra); tmem_ld16_issue(tS + (c0 + cs) * 16, rb);
-        chunk_exp_pack<false, 16>(ra, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed); tmem_st4(tP + c0 * 4, packed);
+        chunk_exp_pack<false, 16, kPolicy>(ra, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed, p_cap); tmem_st4(tP + c0 * 4, packed);
         tmem_ld_fence(rb); tmem_ld16_issue(tS + (c0 + 2 * cs) * 16, ra);
-        chunk_exp_pack<false, 16>(rb, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed); tmem_st4(tP + (c0 + cs) * 4, packed);
+        chunk_exp_pack<false, 16, kPolicy>(rb, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed, p_cap); tmem_st4(tP + (c0 + cs) * 4, packed);
         tmem_ld_fence(ra); tmem_ld16_issue(tS + (c0 + 3 * cs) * 16, rb);
-        chunk_exp_pack<false, 16>(ra, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed); tmem_st4(tP + (c0 + 2 * cs) * 4, packed);
+        chunk_exp_pack<false, 16, kPolicy>(ra, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed, p_cap); tmem_st4(tP + (c0 + 2 * cs) * 4, packed);
         tmem_ld_fence(rb);
-        chunk_exp_pack<false, 16>(rb, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed); tmem_st4(tP + (c0 + 3 * cs) * 4, packed);
+        chunk_exp_pack<false, 16, kPolicy>(rb, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed, p_cap); tmem_st4(tP + (c0 + 3 * cs) * 4, packed);
       } else {
         tmem_ld_fence(ra);
 #pragma unroll 1
         for (int i = 0; i < 4; ++i) {
           const int c = c0 + i * cs;
           if (i > 0) { tmem_ld16_issue(tS + c * 16, ra); tmem_ld_fence(ra); }
-          chunk_exp_pack<true, 16>(ra, (mwords[c >> 1] >> ((c & 1) * 16)) & 0xFFFFu, k.c2, k.neg_hi, k.p_mul_f, sum, packed);
+          chunk_exp_pack<true, 16, kPolicy>(ra, (mwords[c >> 1] >> ((c & 1) * 16)) & 0xFFFFu, k.c2, k.neg_hi, k.p_mul_f, sum, packed, p_cap);
           tmem_st4(tP + c * 4, packed);
         }
       }
@@ -509,7 +545,7 @@ __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D
 // ---------------------------------------------------------------------------------------------- merge role
 // One thread = one half (D/2 columns) of the fp32 running output row of one query row, plus the running
 // maximum and the running sum of that row (kept by both threads of the row).
-template <int D>
+template <int D, bool kPolicy>
 __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>::kStagesK, FwdCfg<D>::kStagesV>* ctl, const uint32_t tmem_base,
                                            const int first_unit, const int unit_step) {
   constexpr int DH = D / 2;
@@ -537,6 +573,8 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
 #pragma unroll
     for (int i = 0; i < DH / 2; ++i) o2[i] = make_float2(0.f, 0.f);
     float m_run = -INFINITY, l_run = 0.f;
+    int imax_run = INT_MIN;                                 // statistics launch: biased integer row maximum over all tiles
+    const bool stats_only = !kPolicy && p.row_stats_out != nullptr;
 
 #pragma unroll 1
     for (int j = 0; j < n_live; ++j) {
@@ -548,13 +586,17 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
         return;
       }
       // ---- merge of tile statistics (inc/fmha_i8.cuh:301-304)
-      const float m_tile = ctl->st_m[slot][row];
-      const float l_tile = ctl->st_f[slot][row] * (ctl->st_s0[slot][row] + ctl->st_s1[slot][row]);
-      const float m_new = fmaxf(m_run, m_tile);
-      const float e_old = __expf(m_run - m_new);                       // 0 on the first tile (m_run = -inf)
-      const float e_cur = clear_low2(__expf(m_tile - m_new));          // 22 significant bits: kMagic*e_cur is exact
-      l_run = fmaf(e_old, l_run, e_cur * l_tile);
-      m_run = m_new;
+      float e_old = 1.f, e_cur = 1.f;                                  // policy launch: every tile of a row has the same scale
+      if (!kPolicy) {
+        const float m_tile = ctl->st_m[slot][row];
+        const float l_tile = ctl->st_f[slot][row] * (ctl->st_s0[slot][row] + ctl->st_s1[slot][row]);
+        const float m_new = fmaxf(m_run, m_tile);
+        e_old = __expf(m_run - m_new);                                 // 0 on the first tile (m_run = -inf)
+        e_cur = clear_low2(__expf(m_tile - m_new));                    // 22 significant bits: kMagic*e_cur is exact
+        l_run = fmaf(e_old, l_run, e_cur * l_tile);
+        m_run = m_new;
+        imax_run = max(imax_run, ctl->st_i[slot][row]);
+      }
       const float es = p.o_sign * e_cur;                               // the accumulator holds o_sign * (P.V)
       const float2 neg_ec = make_float2(es, es), e_bias = make_float2(-es * kMagic, -es * kMagic);
       const float2 e_old2 = make_float2(e_old, e_old);
@@ -568,7 +610,7 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
       }
       tc_fence_after();
       if (quad == 0) FMHA_STAMP(8 + 2 * ch, g);
-      {
+      if (!stats_only) {
         // output column c of this step: tensor-memory column of 16-column chunk i of MY half
         auto chunk_col = [&](int i) -> uint32_t {
           const int c = ch * DH + i * 16;                                   // output column
@@ -592,6 +634,20 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
       if (quad == 0) FMHA_STAMP(9 + 2 * ch, g);
     }
     g0 += static_cast<uint32_t>(n_live);
+
+    // ---- statistics launch: the row's maximum and exp-sum over all keys, for the policy launch that follows
+    if (stats_only) {
+      if (ch == 0 && q_row < p.Sq)
+        p.row_stats_out[static_cast<int64_t>(geo.bh_local) * p.Sq + q_row] =
+            make_float2(__int_as_float(n_live > 0 ? imax_run : static_cast<int>(kMagicBits)), n_live > 0 ? l_run : 0.f);
+      continue;
+    }
+    if (kPolicy) {
+      // the accumulated integer sum becomes the output through one factor per row: out_mul (/ l for the per-row policy)
+      float l_row = 0.f;
+      if (q_row < p.Sq) l_row = __ldg(&p.row_stats_in[static_cast<int64_t>(geo.bh_local) * p.Sq + q_row]).y;
+      l_run = (p.p_static_mul != 0.f) ? (l_row > 0.f ? 1.f : 0.f) : l_row;
+    }
 
     // ---- calibration mode: only the largest magnitude of the unquantised output is wanted (the reference
     //      takes o_amax from its fp32 CPU result, test_fmha_i8.cpp:161)
@@ -827,7 +883,9 @@ __device__ __forceinline__ void o_issuer_role(const FwdParams& p, FwdCtl<FwdCfg<
 }
 
 // Persistent kernel: gridDim.x = min(units, SMs) CTAs; CTA b processes units b, b + gridDim.x, ...
-template <int D>
+// kPolicy: the launch that applies a whole-row P scaling policy from row statistics (see FwdParams::row_stats_in);
+// the product default, and the statistics launch, are kPolicy = false.
+template <int D, bool kPolicy>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
@@ -895,10 +953,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   // phase of an info barrier = (it / kInfoBufs) & 1; `g` counts its steps (live key tiles) across units.
   if (warp >= kWarpSoftmax0) {
     setmaxnreg_dec<FwdRegs<D>::kSoftmax>();
-    softmax_role<D>(p, ctl, tmem_base, first_unit, unit_step);
+    softmax_role<D, kPolicy>(p, ctl, tmem_base, first_unit, unit_step);
   } else if (warp >= kWarpMerge0) {
     setmaxnreg_inc<FwdRegs<D>::kMerge>();
-    merge_role<D>(p, ctl, tmem_base, first_unit, unit_step);
+    merge_role<D, kPolicy>(p, ctl, tmem_base, first_unit, unit_step);
   } else {
     if (FwdRegs<D>::kOther < kLaunchRegs) setmaxnreg_dec<FwdRegs<D>::kOther>(); else setmaxnreg_inc<FwdRegs<D>::kOther>();
     if (warp == kWarpLoad) {

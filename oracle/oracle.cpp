@@ -263,6 +263,71 @@ void oracle_q128(const int8_t* q, const int8_t* k, const int8_t* v, const int8_t
   oracle_q128_x(q, k, v, mask, B, H, S, S, D, amax, 128, rows, n_rows, out, n_threads);
 }
 
+// Whole-row scaling policies for the 8-bit P, restated from the reference's accuracy study
+// (fmha_i8_quant_deviation.py:57-121; the same three policies are swept over the sequence length in
+// fmha_i8_quant_error_seqlen.py:21-130).  The study works on one 512 x 64 problem in numpy without tiles:
+//   scores        f_s = i32_s * q_amax/127 * k_amax/127 / sqrt(D)                       (:57-58)
+//   probabilities f_p = exp(f_s - row max) / row sum, the row NORMALISED                  (:63-68)
+//   quantisation  P8 = clip(round(f_p * 127 / p_amax), 0, 127) as unsigned bytes          (:38-43, SOFTMAX_QUANT_SCALE = 127 at :7)
+//   output        f_o = (P8 . V8) * p_amax/127 * v_amax/127                              (:72, :98, :118)
+// with p_amax = 1 ("worst case", :61), = the largest probability of the whole problem ("static", :86; the number the
+// reference test computes as s_max, test_fmha_i8.cpp:152) or = the largest probability of the row ("dynamic",
+// :104-112).  Here: policy 1 = per row, 2 = static with p_amax = amax[4], 3 = worst case (p_amax = 1).
+// Kept from the device path so that the result can be compared with it: the order in which the score scale is
+// applied (inc/fmha_i8.cuh:72,196), the mask semantics (masked key: p = 0; row without keys: zeros) and the
+// requantisation of the output to int8 against o_amax with round-half-even (inc/fmha_i8.cuh:318-328).
+void oracle_policy_x(const int8_t* q, const int8_t* k, const int8_t* v, const int8_t* mask,
+                     int B, int H, int Sq, int S, int D, const float* amax5, int policy,
+                     const int64_t* rows, int64_t n_rows, int8_t* out, int n_threads) {
+  const float levels = 127.f;
+  const float row_scale = 1.0f / newton_sqrt(static_cast<float>(D));
+  const float scale_qk = amax5[0] * amax5[1] / (127.f * 127.f);
+  const int64_t total = rows ? n_rows : static_cast<int64_t>(B) * H * Sq;
+  const int chunks = static_cast<int>(std::min<int64_t>(total, 4096));
+  parallel_for(chunks, n_threads, [=](int c0) {
+    std::vector<float> e(S);
+    std::vector<int32_t> ot(D);
+    for (int64_t idx = c0; idx < total; idx += chunks) {
+      const int64_t r = rows ? rows[idx] : idx;
+      const int64_t bh = r / Sq;
+      const int i = static_cast<int>(r % Sq);
+      const int b = static_cast<int>(bh / H);
+      const int8_t* qr = q + (bh * Sq + i) * D;
+      const int8_t* kb = k + bh * S * D;
+      const int8_t* vb = v + bh * S * D;
+      const int8_t* mb = mask + static_cast<int64_t>(b) * S;
+      float m = -INFINITY;
+      for (int c = 0; c < S; ++c) {
+        int32_t acc = 0;
+        const int8_t* kr = kb + static_cast<int64_t>(c) * D;
+        for (int d = 0; d < D; ++d) acc += static_cast<int32_t>(qr[d]) * static_cast<int32_t>(kr[d]);
+        e[c] = (row_scale * static_cast<float>(acc)) * scale_qk;
+        if (mb[c] == 0) m = std::max(m, e[c]);
+      }
+      float l = 0.f, p_max = 0.f;
+      for (int c = 0; c < S; ++c) {
+        e[c] = (mb[c] != 0) ? 0.f : expf(e[c] - m);
+        l += e[c];
+      }
+      int8_t* dst = out + (rows ? idx : r) * D;
+      if (!(l > 0.f)) { std::memset(dst, 0, D); continue; }
+      for (int c = 0; c < S; ++c) { e[c] = e[c] / l; p_max = std::max(p_max, e[c]); }          // :64-68 (:108-111)
+      const float p_amax = policy == 1 ? p_max : (policy == 2 ? amax5[4] : 1.0f);
+      const float scale = levels / p_amax;                                                       // :39
+      std::fill(ot.begin(), ot.end(), 0);
+      for (int c = 0; c < S; ++c) {
+        const int32_t p8 = clamp_round_even_i32(e[c] * scale, 0.f, levels);                      // :41
+        if (p8 == 0) continue;
+        const int8_t* vr = vb + static_cast<int64_t>(c) * D;
+        for (int d = 0; d < D; ++d) ot[d] += p8 * static_cast<int32_t>(vr[d]);
+      }
+      const float back = (p_amax / levels) * (amax5[2] / 127.f);                                 // :72 / :98 / :118
+      const float to_int8 = 127.f / amax5[3];
+      for (int d = 0; d < D; ++d) dst[d] = clamp_round_even((static_cast<float>(ot[d]) * back) * to_int8, -127.f, 127.f);
+    }
+  });
+}
+
 // Emulation of the reference CUDA kernel AS WRITTEN (inc/fmha_i8.cuh:87-332, the 128-key-tile variants), thread
 // for thread where it matters, for pinning tier C against bytes the reference kernel really produces.
 // It differs from tier C in exactly two places, both selectable so that each difference can be shown on its own:

@@ -65,6 +65,8 @@ def lib():
                                               _f32p, _c.POINTER(_c.c_float), _c.c_int]
         L.oracle_q128_x.argtypes = [_i8p, _i8p, _i8p, _i8p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _f32p,
                                     _c.c_int, _c.c_void_p, _c.c_int64, _i8p, _c.c_int]
+        L.oracle_policy_x.argtypes = [_i8p, _i8p, _i8p, _i8p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _f32p,
+                                      _c.c_int, _c.c_void_p, _c.c_int64, _i8p, _c.c_int]
         L.oracle_refkernel_emulate.argtypes = [_i8p, _i8p, _i8p, _i8p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _f32p,
                                                _c.c_int, _c.c_int, _i8p, _c.c_int]
         L.oracle_row_scale.restype = _c.c_float
@@ -153,6 +155,28 @@ def row_scale(D):
 # ----------------------------------------------------------------------------------------------
 def ref_cpu_available(native=False):
     return os.path.exists(os.path.join(HERE, "_ref", "libref_cpu_native.so" if native else "libref_cpu.so"))
+
+
+POLICY_ROW, POLICY_STATIC, POLICY_WORST = 1, 2, 3
+
+
+def policy(q8, k8, v8, mask, amax5, which, rows=None, threads=None):
+    """The whole-row P scaling policies of the reference's accuracy study (fmha_i8_quant_deviation.py:57-121) with int8
+    output: which = POLICY_ROW ("dynamic"), POLICY_STATIC (p_amax = amax5[4] = s_max) or POLICY_WORST (p_amax = 1).
+    q8 int8 [B,H,Sq,D]; k8, v8 int8 [B,H,Sk,D]; mask int8 [B,Sk]; amax5 = (q, k, v, o, s_max).  rows as in q128()."""
+    B, H, Sq, D = q8.shape
+    Sk = k8.shape[2]
+    a = np.asarray(amax5, np.float32)
+    assert a.size == 5 and mask.shape == (B, Sk)
+    args = [np.ascontiguousarray(x, np.int8) for x in (q8, k8, v8, mask)]
+    if rows is None:
+        out = np.empty((B, H, Sq, D), np.int8)
+        lib().oracle_policy_x(*args, B, H, Sq, Sk, D, a, int(which), None, 0, out, threads or n_threads_default())
+    else:
+        rows = np.ascontiguousarray(rows, np.int64)
+        out = np.empty((rows.size, D), np.int8)
+        lib().oracle_policy_x(*args, B, H, Sq, Sk, D, a, int(which), rows.ctypes.data, rows.size, out, threads or n_threads_default())
+    return out
 
 
 def refkernel_emulate(q8, k8, v8, mask, amax4, mask_minus_1e6=True, shuffle_as_written=True, threads=None):
