@@ -277,6 +277,7 @@ int infer_x_impl(void* stream, const float amax[5], const Shape& sh, const void*
   }
   p.mask = static_cast<const int8_t*>(mask);
   p.o = static_cast<int8_t*>(o);
+  p.o_wide = aligned(o, 32) ? 1 : 0;
   p.S = sh.Sk;
   p.Sq = sh.Sq;
   p.H = sh.H;

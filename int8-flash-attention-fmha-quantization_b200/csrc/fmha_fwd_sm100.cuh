@@ -12,11 +12,12 @@
 //   two chains = the softmax warps form two teams; steps alternate between them (chain = g & 1).
 //   S buffers  = S = Q.K^T of step g lands in accumulator g % n of tensor memory (n = 3 at head_dim 128, 4 at
 //                head_dim 64), issued as soon as that accumulator is free, i.e. several steps ahead of the
-//                softmax warps.  The same accumulator then carries the step through the rest of its life: the
-//                softmax threads overwrite the two ends of it with the 8-bit P row, and P.V of the step writes
-//                its partial output into the 96 columns in between (head_dim 128: 96 columns there and the last
-//                32 in a small annex).  So every step in flight owns its whole set of buffers and no role ever
-//                waits for another STEP's buffer, only for its own step's previous stage.
+//                softmax warps.  The same accumulator then carries the step through the rest of its life: once the
+//                softmax threads have consumed S, P.V of the step writes its partial output there.  The 8-bit P row
+//                goes into a 32-column annex of the accumulator (head_dim 128) or over the two ends of the
+//                accumulator itself (head_dim 64, where the partial output needs only 64 columns in between).  So
+//                every step in flight owns its whole set of buffers and no role ever waits for another STEP's
+//                buffer, only for its own step's previous stage.
 //
 //   warp 0       loader: TMA brings Q (once per unit, in a small ring) and rings of K and of V tiles into
 //                swizzled shared memory, running ahead into the next units.
@@ -35,8 +36,9 @@
 //   warps 12-27  softmax: warps 12-19 serve chain 0, warps 20-27 chain 1.  TWO threads share one query row:
 //                thread `half` owns keys [64*half, 64*half+64) of the tile.  Each reads its part of S twice
 //                (integer max, then exp + requantise), the two exchange their maxima through shared memory,
-//                and each writes its 8-bit P values over columns it has already consumed (the lower half row
-//                walks up and leaves P in columns [0,16), the upper one walks down and leaves it in [112,128)).
+//                and each writes its 8-bit P values into the annex or, at head_dim 64, over columns it has already
+//                consumed (the lower half row walks up and leaves P in columns [0,16), the upper one walks down
+//                and leaves it in [112,128)).
 //                These threads hold no output row, so they are light (64 registers).
 //
 // The bias: every accumulator is first written by a one-step fp16 MMA whose operands hold 4096 and
@@ -45,9 +47,10 @@
 // ever converts integers to floats: one fused multiply-add turns the raw accumulator into the
 // exponent argument (or into the rescaled partial output).
 //
-// Tensor memory (512 columns x 128 lanes x 32 bit): accumulator b at columns [128 b, 128 b + 128); at head_dim
-// 128 annex b at [384 + 32 b, 384 + 32 b + 32).  Inside an accumulator, after the softmax: P of keys 0-63 in
-// columns [0,16), P of keys 64-127 in columns [112,128) (four int8 per column), partial output in [16, 16+min(D,96)).
+// Tensor memory (512 columns x 128 lanes x 32 bit): accumulator b at columns [128 b, 128 b + 128).
+// head_dim 128: annex b at [384 + 32 b, 384 + 32 b + 32) holds P (four int8 per column, keys in order), the partial
+// output fills the accumulator.  head_dim 64: inside the accumulator, P of keys 0-63 in columns [0,16), P of keys
+// 64-127 in columns [112,128), partial output in [16,80).
 //
 // Numerics kept equal to the reference kernel within the test tolerance: the running output is kept
 // unnormalised (divided by the row sum once at the end) instead of renormalised after every tile,
@@ -108,13 +111,23 @@ constexpr int kWarpScan = 2;
 constexpr int kWarpMmaO = 3;
 constexpr int kWarpMerge0 = 4;
 constexpr int kWarpSoftmax0 = kWarpMerge0 + kMergeWarps;
-constexpr int kSBufsMax = 4;
-// S accumulators in tensor memory: three of 128 columns plus three 32-column annexes at head_dim 128 (480 columns),
-// four at head_dim 64, where the partial output fits between the P bytes of its own accumulator (512 columns)
+// Tensor memory.  A buffer set is one 128-column accumulator that first holds S of a step and then, once the softmax
+// threads have consumed it, the partial output P.V of the same step.
+//   head_dim 128: three sets (384 columns) plus three 32-column annexes that take the P bytes of the step (480 columns);
+//                 the partial output covers the whole accumulator, so P.V is one group of MMAs with N = 128.
+//   head_dim 64:  four sets (512 columns); the P bytes stay inside the accumulator, keys 0-63 in its first 16 columns and
+//                 keys 64-127 in its last 16, and the 64-column partial output sits between them from column 16 on.
+//                 (Three sets with annexes, as at head_dim 128, run 5 % faster on sequences of 2048 and more and 5 %
+//                 slower at sequence length 512, where the S issuer works several units ahead.)
 template <int D> struct SBufs { static constexpr int n = (D == 128) ? 3 : 4; };
-constexpr int kOOff = 16;            // the partial output of a step starts at this column of the step's S accumulator ...
-constexpr int kOMain = 96;           // ... and may use this many columns there (between the two blocks of P bytes);
-constexpr int kOAnnex = 32;          // head_dim 128 puts its last 32 output columns into an annex of that accumulator
+constexpr int kSBufsMax = 4;
+template <int D> struct PLayout {
+  static constexpr bool kAnnex = (D == 128);
+  static constexpr int kOOff = kAnnex ? 0 : 16;        // first column of the partial output inside its accumulator
+  static constexpr int kAnnexCols = 32;                // 128 keys x 1 byte
+  // column (relative to the accumulator of the set, or to the set's annex) of the P bytes of keys [32 kk, 32 kk + 32)
+  __host__ __device__ static constexpr int p_col(int kk) { return kAnnex ? 8 * kk : (kk >> 1) * 112 + (kk & 1) * 8; }
+};
 constexpr int kInfoBufs = 4;         // units whose mask information is resident at once
 constexpr int kInfoConsumers = 3 + kSoftmaxWarps + kMergeWarps;   // loader, two issuers, softmax and merge warps release an info buffer once each
 // setmaxnreg moves registers inside the CTA's own launch allocation (registers per thread at launch x
@@ -154,6 +167,7 @@ template <int D> struct FwdCfg {
 struct FwdParams {
   const int8_t* mask;   // [B,S] whole mask
   int8_t* o;            // first head of the slice
+  int o_wide;           // o is 32-byte aligned: the epilogue may use 32-byte stores
   int S;                // keys per head (seq_len; seq_len_k when queries and keys differ in number)
   int Sq;               // query rows per head (== S for self-attention)
   int H, bh_begin, bh_count, q_tiles;
@@ -450,12 +464,14 @@ __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D
       // the 64 mask bits of my keys (only looked at on the mixed path)
       const uint32_t* mwords = &info->maskbits[4 * info->live[j] + 2 * half];
 
-      // Order of my four 16-column chunks: the lower half row walks up and leaves its P bytes in the first 16 of its
-      // 64 columns, the upper half row walks DOWN and leaves them in the last 16, always over columns it has already
-      // consumed.  What stays untouched in between, columns [16,112) of the accumulator, is where P.V of this step
-      // will put the partial output.
+      // Order of my four 16-column chunks: the lower half row walks up, the upper half row walks DOWN.  At head_dim 64
+      // that lets each leave its P bytes over columns it has already consumed (the first 16 and the last 16 of the
+      // accumulator); columns [16,112) stay untouched, and P.V of this step puts the partial output there.
       const int c0 = half ? 3 : 0, cs = half ? -1 : 1;                 // first chunk and direction
-      const uint32_t tP = tS + (half ? 48u : 0u);                      // my 16 columns of P
+      // my 16 columns of P: inside the accumulator (head_dim 64) or in the annex of the buffer set (head_dim 128)
+      const uint32_t tP = PLayout<D>::kAnnex
+          ? tS0 - static_cast<uint32_t>(half * kHalf) + SBufs<D>::n * kTile + sb * PLayout<D>::kAnnexCols + static_cast<uint32_t>(half * 16)
+          : tS + (half ? 48u : 0u);
 
       uint32_t ra[16], rb[16];
       RowConsts k;
@@ -602,8 +618,7 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
       const float2 e_old2 = make_float2(e_old, e_old);
 
       // ---- drain my half of O~ = bias -/+ (P8 . V) into the fp32 running row.  The partial output of step g lives in
-      //      the accumulator S(g) came from: columns [16, 16 + min(D, 96)) of it, and for head_dim 128 the last 32
-      //      output columns in a 32-column annex of that accumulator.
+      //      the accumulator S(g) came from: all of it at head_dim 128, columns [16,80) at head_dim 64.
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&ctl->o_full[sb]), (g / SBufs<D>::n) & 1u, abort_flag))) {
         raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_O_READY, g);
         return;
@@ -612,10 +627,7 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
       if (quad == 0) FMHA_STAMP(8 + 2 * ch, g);
       if (!stats_only) {
         // output column c of this step: tensor-memory column of 16-column chunk i of MY half
-        auto chunk_col = [&](int i) -> uint32_t {
-          const int c = ch * DH + i * 16;                                   // output column
-          return (c < kOMain) ? (t_lane + sb * kTile + kOOff + c) : (t_lane + SBufs<D>::n * kTile + sb * kOAnnex + (c - kOMain));
-        };
+        auto chunk_col = [&](int i) -> uint32_t { return t_lane + sb * kTile + PLayout<D>::kOOff + ch * DH + i * 16; };
         // two loads in flight at a time: a round trip to tensor memory costs more than folding a chunk in
         uint32_t ra[16], rb[16];
         tmem_ld16_issue(chunk_col(0), ra);
@@ -664,7 +676,7 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
       continue;
     }
 
-    // ---- epilogue (inc/fmha_i8.cuh:318-332): normalise, requantise, 16-byte stores
+    // ---- epilogue (inc/fmha_i8.cuh:318-332): normalise, requantise, store
     if (q_row < p.Sq) {
       const float inv = (n_live > 0 && l_run > 0.f) ? 1.0f / l_run : 0.f;
       int8_t* dst = p.o + (static_cast<int64_t>(geo.bh_local) * p.Sq + q_row) * D + ch * DH;
@@ -672,9 +684,10 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
       // integer), bytes gathered with PRMT: conversions and shifts would cost three times the issue cycles
       const float2 inv2 = make_float2(inv, inv), sc2 = make_float2(p.scale_v_out, p.scale_v_out);
       const float2 zero2 = make_float2(0.f, 0.f), magic2 = make_float2(kMagic, kMagic);
+      uint32_t wide[8];
 #pragma unroll
       for (int c = 0; c < DH / 16; ++c) {
-        uint32_t wds[4];
+        uint32_t* wds = &wide[(c & 1) * 4];
 #pragma unroll
         for (int gq = 0; gq < 4; ++gq) {
           float2 a = __ffma2_rn(sc2, __ffma2_rn(o2[c * 8 + gq * 2], inv2, zero2), zero2);        // scale_v_out * (o * inv), each product rounded
@@ -685,7 +698,16 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
           wds[gq] = __byte_perm(__byte_perm(__float_as_uint(ya.x), __float_as_uint(ya.y), 0x0040),
                                 __byte_perm(__float_as_uint(yb.x), __float_as_uint(yb.y), 0x0040), 0x5410);
         }
-        *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+        // 32-byte stores: a warp's rows are 128 (or 64) bytes apart, so every store touches 32 lines whatever its
+        // width, and the 16-byte version of this loop cost 5 % of the whole kernel at head_dim 128
+        if (c & 1) {
+          if (p.o_wide) {
+            st_global_v8(dst + (c - 1) * 16, wide);
+          } else {
+            *reinterpret_cast<uint4*>(dst + (c - 1) * 16) = make_uint4(wide[0], wide[1], wide[2], wide[3]);
+            *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(wide[4], wide[5], wide[6], wide[7]);
+          }
+        }
       }
     }
   }
@@ -830,13 +852,10 @@ __device__ __forceinline__ void o_issuer_role(const FwdParams& p, FwdCtl<FwdCfg<
   using Cfg = FwdCfg<D>;
   constexpr uint32_t NV = Cfg::kStagesV;
   volatile int* abort_flag = &ctl->abort;
-  constexpr int NMain = D > kOMain ? kOMain : D, NAnnex = D > kOMain ? D - kOMain : 16;
-  static_assert(NAnnex <= kOAnnex, "annex too small");
-  // O = P.V : V is an MN-major operand; N = 96 + 32 output columns for head_dim 128, 64 for head_dim 64
-  const uint32_t idesc_main = p.p_unsigned ? make_idesc_i8(NMain, true, true) : make_idesc_i8(NMain, true, false);
-  const uint32_t idesc_annex = p.p_unsigned ? make_idesc_i8(NAnnex, true, true) : make_idesc_i8(NAnnex, true, false);
+  // O = P.V : V is an MN-major operand; one group of MMAs with N = head_dim output columns
+  const uint32_t idesc_o = p.p_unsigned ? make_idesc_i8(D, true, true) : make_idesc_i8(D, true, false);
 #if FMHA_PV_BIAS_MMA
-  constexpr uint32_t idesc_bias_main = make_idesc_f16(NMain), idesc_bias_annex = make_idesc_f16(NAnnex);
+  constexpr uint32_t idesc_bias = make_idesc_f16(D);
   const uint64_t d_bias_a = make_smem_desc_noswizzle(bias_a_smem, 128, 256);
   const uint64_t d_bias_b = make_smem_desc_noswizzle(bias_b_smem, 128, 256);
 #endif
@@ -856,25 +875,21 @@ __device__ __forceinline__ void o_issuer_role(const FwdParams& p, FwdCtl<FwdCfg<
       FMHA_STAMP(13, g);
       if (!issuer_wait<true>(err, smem_u32(&ctl->v_full[stage]), (g / NV) & 1u, FMHA_I8_DEV_WAIT_V_LOAD, g, abort_flag)) { ok = false; break; }
       const uint64_t dv = make_smem_desc(v_smem + stage * Cfg::kTileBytes, D);
-      const uint32_t tP = tmem_base + sb * kTile;
+      const uint32_t tS = tmem_base + sb * kTile;
+      const uint32_t tP = PLayout<D>::kAnnex ? tmem_base + SBufs<D>::n * kTile + sb * PLayout<D>::kAnnexCols : tS;
+      const uint32_t tO = tS + PLayout<D>::kOOff;
       tc_fence_after();
-      // The accumulator of this step is the part of S(g)'s own buffer that holds no P bytes (free since the softmax
-      // threads have read S(g)) plus, for head_dim 128, that buffer's annex (free since S(g) could be issued at all).
+      // The accumulator of this step is S(g)'s own buffer (free since the softmax threads have read S(g)), minus the
+      // columns that hold P bytes at head_dim 64.
       if (elect_one()) {
-#pragma unroll
-      for (int part = 0; part < (D > kOMain ? 2 : 1); ++part) {
-        const int col0 = part * kOMain;                                  // first output column of this part
-        const uint32_t tO = part == 0 ? (tP + kOOff) : (tmem_base + SBufs<D>::n * kTile + sb * kOAnnex);
-        const uint32_t idesc_o = part == 0 ? idesc_main : idesc_annex;
 #if FMHA_PV_BIAS_MMA
-        mma_f16_ss(tO, d_bias_a, d_bias_b, part == 0 ? idesc_bias_main : idesc_bias_annex, 0u);      // accumulator := 0x4B400000
+        mma_f16_ss(tO, d_bias_a, d_bias_b, idesc_bias, 0u);      // accumulator := 0x4B400000
 #endif
 #pragma unroll
-        for (int kk = 0; kk < kTile / 32; ++kk)     // keys 32 kk ...: P bytes of keys 0-63 at columns 0-15, of keys 64-127 at columns 112-127
-          mma_i8_ts(tO, tP + (kk >> 1) * 112 + (kk & 1) * 8, desc_advance(dv, kk * 32 * D + col0), idesc_o, (FMHA_PV_BIAS_MMA || kk > 0) ? 1u : 0u);
-      }
-      mma_commit(smem_u32(&ctl->o_full[sb]));
-      mma_commit(smem_u32(&ctl->v_empty[stage]));
+        for (int kk = 0; kk < kTile / 32; ++kk)
+          mma_i8_ts(tO, tP + PLayout<D>::p_col(kk), desc_advance(dv, kk * 32 * D), idesc_o, (FMHA_PV_BIAS_MMA || kk > 0) ? 1u : 0u);
+        mma_commit(smem_u32(&ctl->o_full[sb]));
+        mma_commit(smem_u32(&ctl->v_empty[stage]));
       }
       FMHA_STAMP(14, g);
     }
