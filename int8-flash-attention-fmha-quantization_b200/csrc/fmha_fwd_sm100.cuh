@@ -642,14 +642,20 @@ __device__ __forceinline__ void merge_role(const FwdParams& p, FwdCtl<FwdCfg<D>:
 #pragma unroll
         for (int c = 0; c < DH / 16; c += 2) {
           tmem_ld_fence(ra); tmem_ld_fence(rb);
+          if (c + 2 >= DH / 16) {
+            // the last two chunks are in registers: the accumulator can go back to the S issuer before they are folded in
+            tc_fence_before();
+            mbar_arrive(smem_u32(&ctl->s_free[sb]));
+          }
           drain_chunk<16>(ra, o2 + c * 8, neg_ec, e_bias, e_old2);
           if (c + 2 < DH / 16) tmem_ld16_issue(chunk_col(c + 2), ra);
           drain_chunk<16>(rb, o2 + (c + 1) * 8, neg_ec, e_bias, e_old2);
           if (c + 3 < DH / 16) tmem_ld16_issue(chunk_col(c + 3), rb);
         }
+      } else {
+        tc_fence_before();
+        mbar_arrive(smem_u32(&ctl->s_free[sb]));
       }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&ctl->s_free[sb]));
       if (quad == 0) FMHA_STAMP(9 + 2 * ch, g);
     }
     g0 += static_cast<uint32_t>(n_live);
