@@ -95,9 +95,6 @@ __device__ long long g_trace[48][512];
 #define FMHA_STAMP(slot, idx) do { } while (0)
 #endif
 
-#ifndef FMHA_PIPE2
-#define FMHA_PIPE2 0
-#endif
 constexpr int kTile = 128;           // query rows per tile == keys per tile
 constexpr int kHalf = 64;            // keys per softmax thread
 constexpr int kMaxSeq = 32768;
@@ -360,33 +357,6 @@ __device__ __forceinline__ void chunk_exp_pack(const uint32_t (&r)[N], uint32_t 
   }
 }
 
-// The same arithmetic in two halves, for the software pipeline of pass 2: a group is four scores.
-//   group_exp:  raw accumulator words -> probabilities (2 FFMA2, 4 exponentials)
-//   group_pack: probabilities -> row sums and one word of four P bytes (2 FADD2, 2 FFMA2, 3 byte permutes)
-// An exponential occupies the partition's exponential unit for eight cycles and returns some twenty cycles later;
-// issuing the exponentials of the next group before packing the current one keeps the unit busy from one warp.
-template <bool kCap>
-__device__ __forceinline__ void group_exp(const uint32_t r0, const uint32_t r1, const uint32_t r2, const uint32_t r3, const float2 c2,
-                                          const float2 neg_hi, const float p_cap, float (&e)[4]) {
-  const float2 a01 = __ffma2_rn(make_float2(__uint_as_float(r0), __uint_as_float(r1)), c2, neg_hi);
-  const float2 a23 = __ffma2_rn(make_float2(__uint_as_float(r2), __uint_as_float(r3)), c2, neg_hi);
-  e[0] = ex2_approx(a01.x); e[1] = ex2_approx(a01.y); e[2] = ex2_approx(a23.x); e[3] = ex2_approx(a23.y);
-  if (kCap) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) e[i] = fminf(e[i], p_cap);
-  }
-}
-__device__ __forceinline__ uint32_t group_pack(const float (&e)[4], const float2 p_mul_f, float2 (&sum)[2]) {
-  const float2 magic2 = make_float2(kMagic, kMagic);
-  const float2 p01 = make_float2(e[0], e[1]), p23 = make_float2(e[2], e[3]);
-  sum[0] = __fadd2_rn(sum[0], p01);
-  sum[1] = __fadd2_rn(sum[1], p23);
-  const float2 y01 = __ffma2_rn(p01, p_mul_f, magic2);      // low byte = the two's-complement P8
-  const float2 y23 = __ffma2_rn(p23, p_mul_f, magic2);
-  return __byte_perm(__byte_perm(__float_as_uint(y01.x), __float_as_uint(y01.y), 0x0040),
-                     __byte_perm(__float_as_uint(y23.x), __float_as_uint(y23.y), 0x0040), 0x5410);
-}
-
 // Constants of one row of one tile, derived from the biased integer row maximum.
 struct RowConsts {
   float2 c2, neg_hi, p_mul_f;
@@ -555,32 +525,6 @@ __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D
       float2 sum[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       uint32_t packed[4];
       if (!mixed) {
-#if FMHA_PIPE2
-        float ea[4], eb[4];
-#define FMHA_GE(arr, o, dst) group_exp<kPolicy>(arr[o], arr[o + 1], arr[o + 2], arr[o + 3], k.c2, k.neg_hi, p_cap, dst)
-        tmem_ld_fence(ra); tmem_ld16_issue(tS + (c0 + cs) * 16, rb);
-        FMHA_GE(ra, 0, ea);
-        FMHA_GE(ra, 4, eb);  packed[0] = group_pack(ea, k.p_mul_f, sum);
-        FMHA_GE(ra, 8, ea);  packed[1] = group_pack(eb, k.p_mul_f, sum);
-        FMHA_GE(ra, 12, eb); packed[2] = group_pack(ea, k.p_mul_f, sum);
-        tmem_ld_fence(rb); tmem_ld16_issue(tS + (c0 + 2 * cs) * 16, ra);
-        FMHA_GE(rb, 0, ea);  packed[3] = group_pack(eb, k.p_mul_f, sum); tmem_st4(tP + c0 * 4, packed);
-        FMHA_GE(rb, 4, eb);  packed[0] = group_pack(ea, k.p_mul_f, sum);
-        FMHA_GE(rb, 8, ea);  packed[1] = group_pack(eb, k.p_mul_f, sum);
-        FMHA_GE(rb, 12, eb); packed[2] = group_pack(ea, k.p_mul_f, sum);
-        tmem_ld_fence(ra); tmem_ld16_issue(tS + (c0 + 3 * cs) * 16, rb);
-        FMHA_GE(ra, 0, ea);  packed[3] = group_pack(eb, k.p_mul_f, sum); tmem_st4(tP + (c0 + cs) * 4, packed);
-        FMHA_GE(ra, 4, eb);  packed[0] = group_pack(ea, k.p_mul_f, sum);
-        FMHA_GE(ra, 8, ea);  packed[1] = group_pack(eb, k.p_mul_f, sum);
-        FMHA_GE(ra, 12, eb); packed[2] = group_pack(ea, k.p_mul_f, sum);
-        tmem_ld_fence(rb);
-        FMHA_GE(rb, 0, ea);  packed[3] = group_pack(eb, k.p_mul_f, sum); tmem_st4(tP + (c0 + 2 * cs) * 4, packed);
-        FMHA_GE(rb, 4, eb);  packed[0] = group_pack(ea, k.p_mul_f, sum);
-        FMHA_GE(rb, 8, ea);  packed[1] = group_pack(eb, k.p_mul_f, sum);
-        FMHA_GE(rb, 12, eb); packed[2] = group_pack(ea, k.p_mul_f, sum);
-        packed[3] = group_pack(eb, k.p_mul_f, sum); tmem_st4(tP + (c0 + 3 * cs) * 4, packed);
-#undef FMHA_GE
-#else
         tmem_ld_fence(ra); tmem_ld16_issue(tS + (c0 + cs) * 16, rb);
         chunk_exp_pack<false, 16, kPolicy>(ra, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed, p_cap); tmem_st4(tP + c0 * 4, packed);
         tmem_ld_fence(rb); tmem_ld16_issue(tS + (c0 + 2 * cs) * 16, ra);
@@ -589,7 +533,6 @@ __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D
         chunk_exp_pack<false, 16, kPolicy>(ra, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed, p_cap); tmem_st4(tP + (c0 + 2 * cs) * 4, packed);
         tmem_ld_fence(rb);
         chunk_exp_pack<false, 16, kPolicy>(rb, 0u, k.c2, k.neg_hi, k.p_mul_f, sum, packed, p_cap); tmem_st4(tP + (c0 + 3 * cs) * 4, packed);
-#endif
       } else {
         tmem_ld_fence(ra);
 #pragma unroll 1
