@@ -114,9 +114,10 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
-// One 32-byte store (address 32-byte aligned).
+// One 32-byte store (address 32-byte aligned) that does not allocate a line in L1: the output is written once and
+// never read by this kernel (measured 1.6 % of the C3 launch against the plain store).
 __device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&r)[8]) {
-  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+  asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                ::"l"(ptr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                : "memory");
 }
