@@ -136,10 +136,10 @@ constexpr int kInfoConsumers = 3 + kSoftmaxWarps + kMergeWarps;   // loader, two
 // launch and refuses otherwise); the targets per role (FwdRegs) add up to 28 x 72.
 constexpr int kLaunchRegs = 72;
 template <int D> struct FwdRegs {
-  // head_dim 128: the merge threads hold a 64-register half output row, the single-thread roles run lean
-  // (measured on C3: 104/40 is 2 % faster than 96/56); head_dim 64: the output row is 32 registers and the
-  // single-thread roles, which sit on every unit boundary of the short-sequence shapes, get the rest.
-  static constexpr int kSoftmax = 64, kMerge = (D == 128) ? 104 : 80, kOther = (D == 128) ? 40 : 88;
+  // head_dim 128: the merge threads hold a 64-register half output row, the one-warp roles run lean (measured on C3:
+  // 104/40 is 2 % faster than 96/56).  head_dim 64: the output row is 32 registers; 88/72 is the split at which
+  // ptxas reports no spills at all, and C5 runs 5 % faster with it than with 80/88 or 96/56, which both spill.
+  static constexpr int kSoftmax = 64, kMerge = (D == 128) ? 104 : 88, kOther = (D == 128) ? 40 : 72;
   static_assert(kSoftmaxWarps * kSoftmax + kMergeWarps * kMerge + 4 * kOther <= kFwdWarps * kLaunchRegs,
                 "setmaxnreg targets exceed the CTA's register allocation: the kernel would hang");
   static_assert(kSoftmax <= kLaunchRegs && kMerge >= kLaunchRegs, "the softmax warps give registers, the merge warps gain");
@@ -986,7 +986,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     setmaxnreg_inc<FwdRegs<D>::kMerge>();
     merge_role<D, kPolicy>(p, ctl, tmem_base, first_unit, unit_step);
   } else {
-    if (FwdRegs<D>::kOther < kLaunchRegs) setmaxnreg_dec<FwdRegs<D>::kOther>(); else setmaxnreg_inc<FwdRegs<D>::kOther>();
+    if (FwdRegs<D>::kOther < kLaunchRegs) setmaxnreg_dec<FwdRegs<D>::kOther>();
+    else if (FwdRegs<D>::kOther > kLaunchRegs) setmaxnreg_inc<FwdRegs<D>::kOther>();
     if (warp == kWarpLoad) {
       loader_role<D>(p, ctl, &map_q, &map_k, &map_v, q_smem, k_smem, v_smem, first_unit, unit_step);
     } else if (warp == kWarpMmaS) {
