@@ -922,7 +922,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   using Ctl = FwdCtl<NK, NV>;
   extern __shared__ uint8_t smem_raw[];
   // tiles need 1024-byte alignment (swizzle atoms); the launch reserves the slack
-  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  // (pointer arithmetic on the shared array, not a round trip through an integer: the compiler then knows that everything
+  // derived from it is shared memory and uses 32-bit shared-space loads and stores instead of generic ones)
+  uint8_t* tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* bias_a = tiles + Cfg::kTilesBytesTotal;
   uint8_t* bias_b = bias_a + kBiasBytes;
   Ctl* ctl = reinterpret_cast<Ctl*>(bias_b + kBiasBytes);
