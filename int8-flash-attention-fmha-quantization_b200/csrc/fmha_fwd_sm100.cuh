@@ -454,15 +454,16 @@ __device__ __forceinline__ void softmax_role(const FwdParams& p, FwdCtl<FwdCfg<D
       const uint32_t g = g0 + static_cast<uint32_t>(j);
       const uint32_t sb = g % SBufs<D>::n;                       // S accumulator of this step
       const uint32_t tS = tS0 + sb * kTile;
+      // (read before the wait: none of it depends on S)
+      const bool mixed = info->mixed[j] != 0;
+      // the 64 mask bits of my keys (only looked at on the mixed path)
+      const uint32_t* mwords = &info->maskbits[4 * info->live[j] + 2 * half];
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&ctl->s_full[sb]), (g / SBufs<D>::n) & 1u, abort_flag))) {
         raise_status(abort_flag, p.status, FMHA_I8_DEV_WAIT_S_READY, g);
         return;
       }
       tc_fence_after();
       if (half == 0 && quad == 0) FMHA_STAMP(chain * 4 + 0, n);
-      const bool mixed = info->mixed[j] != 0;
-      // the 64 mask bits of my keys (only looked at on the mixed path)
-      const uint32_t* mwords = &info->maskbits[4 * info->live[j] + 2 * half];
 
       // Order of my four 16-column chunks: the lower half row walks up, the upper half row walks DOWN.  At head_dim 64
       // that lets each leave its P bytes over columns it has already consumed (the first 16 and the last 16 of the
@@ -834,13 +835,14 @@ __device__ __forceinline__ void s_issuer_role(const FwdParams& p, FwdCtl<FwdCfg<
     const uint64_t dq = make_smem_desc(q_smem + qb * Cfg::kTileBytes, D);
     for (int j = 0; j < n_live; ++j, ++g) {
       const uint32_t sb = g % SBufs<D>::n, stage = g % NK;
-      // the accumulator still holds the P bytes of step g - SBufs<D>::n until that step's P.V has completed
-      if (g >= SBufs<D>::n && !issuer_wait(err, smem_u32(&ctl->s_free[sb]), ((g / SBufs<D>::n) - 1) & 1u, FMHA_I8_DEV_WAIT_O_FREE, g, abort_flag)) { ok = false; break; }
-      if (!issuer_wait<true>(err, smem_u32(&ctl->k_full[stage]), (g / NK) & 1u, FMHA_I8_DEV_WAIT_K_LOAD, g, abort_flag)) { ok = false; break; }
-      FMHA_STAMP(15, g);
-      tc_fence_after();
       const uint64_t dk = make_smem_desc(k_smem + stage * Cfg::kTileBytes, D);
       const uint32_t tS = tmem_base + sb * kTile;
+      // K first (it has normally been there for a while), then the accumulator: it still holds the partial output of
+      // step g - n until the merge warps have drained it, and that hand-off is on the step-to-step critical path
+      if (!issuer_wait<true>(err, smem_u32(&ctl->k_full[stage]), (g / NK) & 1u, FMHA_I8_DEV_WAIT_K_LOAD, g, abort_flag)) { ok = false; break; }
+      if (g >= SBufs<D>::n && !issuer_wait(err, smem_u32(&ctl->s_free[sb]), ((g / SBufs<D>::n) - 1) & 1u, FMHA_I8_DEV_WAIT_O_FREE, g, abort_flag)) { ok = false; break; }
+      FMHA_STAMP(15, g);
+      tc_fence_after();
       if (elect_one()) {
         mma_f16_ss(tS, d_bias_a, d_bias_b, idesc_bias_s, 0u);      // accumulator := 0x4B400000
 #pragma unroll
@@ -884,13 +886,14 @@ __device__ __forceinline__ void o_issuer_role(const FwdParams& p, FwdCtl<FwdCfg<
     if (elect_one()) mbar_arrive(smem_u32(&ctl->info_empty[buf]));            // only the tile count is needed here
     for (int j = 0; j < n_live; ++j, ++g) {
       const uint32_t sb = g % SBufs<D>::n, stage = g % NV;
-      if (!issuer_wait(err, smem_u32(&ctl->p_ready[g & 3u]), (g >> 2) & 1u, FMHA_I8_DEV_WAIT_P_READY, g, abort_flag)) { ok = false; break; }
-      FMHA_STAMP(13, g);
-      if (!issuer_wait<true>(err, smem_u32(&ctl->v_full[stage]), (g / NV) & 1u, FMHA_I8_DEV_WAIT_V_LOAD, g, abort_flag)) { ok = false; break; }
       const uint64_t dv = make_smem_desc(v_smem + stage * Cfg::kTileBytes, D);
       const uint32_t tS = tmem_base + sb * kTile;
       const uint32_t tP = PLayout<D>::kAnnex ? tmem_base + SBufs<D>::n * kTile + sb * PLayout<D>::kAnnexCols : tS;
       const uint32_t tO = tS + PLayout<D>::kOOff;
+      // V first (loaded steps ago), then P: the MMAs go out as soon as the last softmax warp has arrived
+      if (!issuer_wait<true>(err, smem_u32(&ctl->v_full[stage]), (g / NV) & 1u, FMHA_I8_DEV_WAIT_V_LOAD, g, abort_flag)) { ok = false; break; }
+      if (!issuer_wait(err, smem_u32(&ctl->p_ready[g & 3u]), (g >> 2) & 1u, FMHA_I8_DEV_WAIT_P_READY, g, abort_flag)) { ok = false; break; }
+      FMHA_STAMP(13, g);
       tc_fence_after();
       // The accumulator of this step is S(g)'s own buffer (free since the softmax threads have read S(g)), minus the
       // columns that hold P bytes at head_dim 64.
