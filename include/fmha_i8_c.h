@@ -6,7 +6,8 @@
  * Conventions shared by every entry point
  *   amax[5] = {q_amax, k_amax, v_amax, o_amax, s_max}   -- FMHAParamI8, inc/fmha_param_i8.h:10-17
  *   desc[4] = {batch_num, seq_len, head_num, head_dim}  -- AttnDataDescriptor, inc/fmha_param_i8.h:3-8
- *   q,k,v,o : int8 [B,H,S,D] contiguous, 16-byte aligned;  mask : int8 [B,S], 4-byte aligned,
+ *   q,k,v,o : int8 [B,H,S,D] contiguous, 16-byte aligned (an o that is 32-byte aligned, as every cudaMalloc'ed
+ *             buffer is, lets the kernel use wider stores: same bytes, about 1 % faster);  mask : int8 [B,S], 4-byte aligned,
  *             non-zero byte = key masked out (inc/cpuSoftmax.hpp:24, inc/fmha_i8.cuh:189-192)
  *   stream  : a cudaStream_t passed as void* (NULL = default stream)
  *   return  : FMHA_I8_OK or a negative FMHA_I8_ERR_* decided on the host before anything is
