@@ -138,13 +138,13 @@ def bind_host_thread_near_gpu(torch, local_rank):
         return None
 
 
-def cpu_baseline(workload, seconds_hint=10.0):
+def cpu_baseline(workload, seconds_hint=10.0, threads=0):
     """The reference project's fp32 CPU path (its unchanged templates, one single-slice call chain per
     head, heads spread over all host threads) on a bounded sample of whole heads of `workload`."""
     import numpy as np
     import __graft_entry__ as ge
     oracle = ge.load_oracle()
-    cores = oracle.n_threads_default()
+    cores = threads if threads > 0 else oracle.n_threads_default()
     w = workload
     per_head_ops = 4.0 * w.S * w.S * w.D
     est_rate = 1.5e9  # ops/s/thread, the order of magnitude of the unvectorised triple loop
@@ -180,7 +180,7 @@ def run_reference_arm(args, workload):
     import numpy as np
     import __graft_entry__ as ge
     oracle = ge.load_oracle()
-    cores = oracle.n_threads_default()
+    cores = args.cpu_threads if args.cpu_threads > 0 else oracle.n_threads_default()
     w = workload
     per_head_ops = 4.0 * w.S * w.S * w.D
     heads = min(w.B * w.H, cores)          # one whole head per host thread and step
@@ -375,6 +375,10 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip parity, reference-GPU baseline, other configs, sustained run")
     ap.add_argument("--e2e-steps", type=int, default=0)
     ap.add_argument("--sustain-seconds", type=float, default=1.2)
+    ap.add_argument("--cpu-threads", type=int, default=0,
+                    help="host threads of the CPU baseline and of --impl reference (0 = all the box has)")
+    ap.add_argument("--check", action="store_true",
+                    help="exit with status 3 when the parity block misses the tolerance (>= 99.9 %% within 1 LSB, none beyond 2)")
     ap.add_argument("--path", default="attention", choices=["attention", "quantize"],
                     help="attention = the forward pass (default); quantize = the device-side abs_max + int8 producer")
     args = ap.parse_args()
@@ -395,6 +399,7 @@ def main():
     import torch
     import torch.distributed as dist
 
+    check_failed = False
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -637,7 +642,7 @@ def main():
                 others[name] = {"error": repr(exc)}
     if rank == 0 and n_gpus == 1 and not args.no_cpu:
         try:
-            cpu = cpu_baseline(w)
+            cpu = cpu_baseline(w, threads=args.cpu_threads)
         except Exception as exc:  # the baseline is a reported extra, never a reason to lose the GPU numbers
             cpu = {"value": None, "unit": UNIT, "cores": None, "kind": "unavailable", "sample": repr(exc)}
 
@@ -658,8 +663,18 @@ def main():
                 "partition_check": partition_check, "weak_replicas": weak_replicas, "sustained": sustained,
                 "parity": parity, "ref_gpu_baseline": ref_gpu, "other_configs": others}
         print(json.dumps(line), flush=True)
+        if args.check:
+            checked = [parity] + [v for v in (others or {}).values() if isinstance(v, dict)]
+            checked = [c for c in checked if c and "within_1_lsb_pct" in c]
+            bad = [c for c in checked if c["within_1_lsb_pct"] < 99.9 or c["max_lsb"] > 2]
+            if bad or not checked:
+                print("bench.py --check: " + ("no parity block was computed (do not combine with --no-extras)" if not checked
+                                               else f"parity outside the tolerance: {bad}"), file=sys.stderr, flush=True)
+                check_failed = True
     if world > 1:
         dist.destroy_process_group()
+    if check_failed:
+        sys.exit(3)
 
 
 if __name__ == "__main__":

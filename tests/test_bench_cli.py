@@ -29,3 +29,13 @@ def test_reference_arm_other_ranks_print_nothing():
                           "--steps", "1", "--warmup", "0"], cwd=ROOT, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stderr[-2000:]
     assert not [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+
+
+def test_reference_arm_honours_cpu_threads():
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--config", "C1",
+                          "--steps", "1", "--warmup", "0", "--cpu-threads", "1"], cwd=ROOT, capture_output=True, text=True,
+                         timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    d = json.loads([ln for ln in out.stdout.splitlines() if ln.startswith("{")][0])
+    assert d["cpu_baseline"]["cores"] == 1
+    assert d["config"]["sampled_heads_per_step"] == 1
